@@ -1,0 +1,168 @@
+"""The step function: run a batch of (request, its next tokens) from the cache and
+return the logits at the wanted places.
+
+`ModelRunner.step` is the only way tokens reach the model: generation, the command
+line, the Python entry point and trace replay all call it.  It reserves pages for
+the new tokens, packs the batch, runs the model once over exactly the tokens it was
+given, and marks them written.  A step made only of single tokens runs as a replayed
+CUDA graph when graphs are enabled (one launch instead of some hundred).
+
+The reference has two forward shapes instead (one whole prompt alone, or N single
+tokens, src/engine.rs:351-401, 405-490) behind `Backend::forward_sample`
+(src/engine.rs:29-46).
+"""
+from __future__ import annotations
+
+from typing import Dict, Hashable, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..errors import CacheError
+from .batch import BatchBuilder, StepContext, StepEntry
+
+
+class ModelRunner:
+    def __init__(self, model, cache, ops, use_graphs: bool = False):
+        self.model = model
+        self.cache = cache
+        self.ops = ops
+        self.device = model.device
+        self.is_cuda = torch.device(self.device).type == "cuda"
+        self.builder = BatchBuilder(cache, ops, self.device, pinned=self.is_cuda)
+        self.use_graphs = use_graphs and self.is_cuda
+        self._graphs: Dict[Tuple[int, int], "_DecodeGraph"] = {}
+        self.steps = 0
+        self.graph_steps = 0
+
+    # ---- requests ----------------------------------------------------------------
+
+    def add_request(self, req: Hashable) -> None:
+        self.cache.add(req)
+
+    def end_request(self, req: Hashable) -> None:
+        self.cache.free(req)
+
+    def computed(self, req: Hashable) -> int:
+        return self.cache.requests[req].computed
+
+    # ---- the step ----------------------------------------------------------------
+
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """float32 logits [wanted, vocab], in the order of the entries and of `want`."""
+        if not entries:
+            return torch.empty((0, self.model.spec.vocab_size), dtype=torch.float32,
+                               device=self.device)
+        seen = set()
+        for e in entries:
+            if e.req in seen:
+                raise ValueError(f"request {e.req!r} appears twice in one step")
+            seen.add(e.req)
+            if not self.cache.has(e.req):
+                raise CacheError(f"request {e.req!r} is not live")
+            total = self.cache.requests[e.req].computed + len(e.tokens)
+            if total > self.model.spec.max_position:
+                raise ValueError(f"request {e.req!r}: {total} tokens exceed the model's "
+                                 f"{self.model.spec.max_position} positions")
+        for e in entries:
+            total = self.cache.requests[e.req].computed + len(e.tokens)
+            if not self.cache.reserve(e.req, total):
+                raise CacheError(f"out of pages: request {e.req!r} needs room for "
+                                 f"{total} tokens")
+        # single tokens first; logits keep the callers' order through logit_rows
+        order = sorted(range(len(entries)), key=lambda i: len(entries[i].tokens) != 1)
+        ordered = [entries[i] for i in order]
+        if order != list(range(len(entries))):
+            logits = self._run(ordered)
+            # rows come out in `ordered` order; put them back in the callers' order
+            counts = [len(e.want) for e in ordered]
+            starts = [0]
+            for c in counts:
+                starts.append(starts[-1] + c)
+            perm = []
+            where = {oi: k for k, oi in enumerate(order)}
+            for i in range(len(entries)):
+                k = where[i]
+                perm.extend(range(starts[k], starts[k + 1]))
+            if perm != list(range(len(perm))):
+                logits = logits[torch.tensor(perm, device=logits.device, dtype=torch.long)]
+        else:
+            logits = self._run(ordered)
+        for e in entries:
+            rc = self.cache.requests[e.req]
+            self.cache.advance(e.req, rc.computed + len(e.tokens))
+        self.steps += 1
+        return logits
+
+    def _run(self, ordered: List[StepEntry]) -> torch.Tensor:
+        if self.use_graphs and all(len(e.tokens) == 1 for e in ordered):
+            return self._run_graph(ordered)
+        ctx = self.builder.build(ordered)
+        return self.model.forward(ctx, self.cache.views())
+
+    # ---- replayed single-token steps ---------------------------------------------------
+
+    def _run_graph(self, ordered: List[StepEntry]) -> torch.Tensor:
+        ps = self.cache.page_size
+        r = len(ordered)
+        bucket = 1 << (r - 1).bit_length()
+        ctx_max = max(self.cache.requests[e.req].computed + 1 for e in ordered)
+        blocks = -(-ctx_max // ps)
+        block_bucket = max(16, 1 << (blocks - 1).bit_length())
+        # every row's logits are produced inside the graph; the wanted ones are picked after
+        full = [StepEntry(e.req, e.tokens, (0,)) for e in ordered]
+        key = (bucket, block_bucket)
+        g = self._graphs.get(key)
+        if g is None:
+            g = _DecodeGraph(self, bucket, block_bucket)
+            self._graphs[key] = g
+        logits = g.run(full)
+        self.graph_steps += 1
+        rows = [i for i, e in enumerate(ordered) for _ in e.want]
+        if rows == list(range(r)):
+            return logits[:r]
+        return logits[torch.tensor(rows, device=logits.device, dtype=torch.long)]
+
+
+class _DecodeGraph:
+    """A captured launch sequence for `bucket` single-token requests whose block tables
+    are `block_bucket` wide.  Its index arrays live at fixed addresses; a step refills
+    them and replays."""
+
+    def __init__(self, runner: ModelRunner, bucket: int, block_bucket: int):
+        self.runner = runner
+        self.bucket = bucket
+        self.block_bucket = block_bucket
+        n_groups = len(runner.cache.groups)
+        words = 16 * bucket + 64 + n_groups * (bucket * (block_bucket + 1) + 8)
+        self.host = torch.empty(words, dtype=torch.int32, pin_memory=True)
+        self.dev = torch.empty(words, dtype=torch.int32, device=runner.device)
+        self.graph = None
+        self.logits = None
+
+    def _build(self, entries) -> StepContext:
+        ctx = self.runner.builder.build(entries, pad_reqs=self.bucket,
+                                        pad_blocks=self.block_bucket,
+                                        buffers=(self.host, self.dev))
+        # launch sizes that depend on the context length must cover every later replay
+        ctx.max_ctx_len = self.block_bucket * self.runner.cache.page_size
+        return ctx
+
+    def run(self, entries) -> torch.Tensor:
+        model, views = self.runner.model, self.runner.cache.views()
+        if self.graph is None:
+            # An eager run over padding only comes first: it initialises the matrix
+            # library for these shapes outside the capture and, being all padding,
+            # writes to no cache (a second run of real tokens would shift the
+            # convolution states twice).
+            warm = self._build([])
+            model.forward(warm, views)
+            torch.cuda.synchronize()
+            ctx = self._build(entries)
+            torch.cuda.synchronize()
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph):
+                self.logits = model.forward(ctx, views)
+        else:
+            self._build(entries)
+        self.graph.replay()
+        return self.logits
