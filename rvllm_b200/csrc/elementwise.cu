@@ -1,0 +1,184 @@
+// Row-wise and element-wise kernels: embedding gather, residual add + RMSNorm,
+// SwiGLU activation, bias add.  Plain references: tests/plain_ops.py.
+#include <stdarg.h>
+
+#include "common.cuh"
+
+static thread_local char g_error[512] = "";
+extern "C" const char* rv_last_error() { return g_error; }
+void rv_set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+}
+
+// ---------------------------------------------------------------------------------
+// Embedding gather: out[t, :] = table[ids[t], :] (* scale), float32 out.
+// Reference counterpart: embed_lookup.cu (one thread per element, float32 table).
+template <typename T>
+__global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
+                             float* __restrict__ out, int hidden, int vocab, float scale) {
+    const int t = blockIdx.x;
+    int id = ids[t];
+    id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+    const T* row = table + (size_t)id * hidden;
+    float* o = out + (size_t)t * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = rv_load(row + i) * scale;
+}
+
+extern "C" int rv_embed(const void* table, int dtype, const int* ids, float* out, int n_tokens,
+                        int hidden, int vocab, float scale, void* stream) {
+    if (n_tokens == 0) return 0;
+    if (n_tokens < 0 || hidden <= 0 || vocab <= 0) RV_FAIL("embed: bad sizes");
+    RV_DISPATCH_DTYPE(dtype, "embed",
+                      (embed_kernel<T><<<n_tokens, 256, 0, (cudaStream_t)stream>>>(
+                          (const T*)table, ids, out, hidden, vocab, scale)));
+    RV_CHECK_LAUNCH("embed");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------
+// Residual add + RMSNorm.  One block per output row; the row is summed into the
+// float32 residual stream, kept in shared memory, and normalised:
+//   x = resid[r] + delta[r];  out = x / sqrt(mean(x^2) + eps) * w
+// With `rows` the block reads row rows[m] and leaves the stream untouched (the final
+// norm over the rows whose logits are wanted).
+// Reference counterparts: add.cu + rmsnorm.cu + f32_to_f16.cu, three launches.
+template <typename TD, typename TO>
+__global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta,
+                                   const float* __restrict__ weight, TO* __restrict__ out,
+                                   const int* __restrict__ rows, int hidden, float eps) {
+    extern __shared__ float row[];
+    __shared__ float scratch[33];
+    const int m = blockIdx.x;
+    const size_t in = (size_t)(rows ? rows[m] : m) * hidden;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        float x = resid[in + i];
+        if (delta) x += rv_load(delta + in + i);
+        if (!rows && delta) resid[in + i] = x;
+        row[i] = x;
+        ss += x * x;
+    }
+    const float total = rv_block_sum(ss, scratch);
+    const float rms = sqrtf(total / (float)hidden + eps);
+    TO* o = out + (size_t)m * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) rv_store(o + i, row[i] / rms * weight[i]);
+}
+
+template <typename TD, typename TO>
+static int add_rmsnorm_launch(float* resid, const void* delta, const float* weight, void* out,
+                              const int* rows, int n_rows, int hidden, float eps,
+                              cudaStream_t stream) {
+    const size_t smem = (size_t)hidden * sizeof(float);
+    if (smem > 200 * 1024) RV_FAIL("add_rmsnorm: width %d exceeds the shared-memory row", hidden);
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(add_rmsnorm_kernel<TD, TO>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) RV_FAIL("add_rmsnorm: %s", cudaGetErrorString(e));
+    }
+    const int threads = hidden >= 1024 ? 256 : 128;
+    add_rmsnorm_kernel<TD, TO><<<n_rows, threads, smem, stream>>>(
+        resid, (const TD*)delta, weight, (TO*)out, rows, hidden, eps);
+    RV_CHECK_LAUNCH("add_rmsnorm");
+    return 0;
+}
+
+extern "C" int rv_add_rmsnorm(float* resid, const void* delta, int delta_dtype, const float* weight,
+                              void* out, int out_dtype, const int* rows, int n_rows, int hidden,
+                              float eps, void* stream) {
+    if (n_rows == 0) return 0;
+    if (n_rows < 0 || hidden <= 0) RV_FAIL("add_rmsnorm: bad sizes");
+    cudaStream_t s = (cudaStream_t)stream;
+    if (delta_dtype == RV_DTYPE_F32 && out_dtype == RV_DTYPE_F32)
+        return add_rmsnorm_launch<float, float>(resid, delta, weight, out, rows, n_rows, hidden, eps, s);
+    if (delta_dtype == RV_DTYPE_BF16 && out_dtype == RV_DTYPE_BF16)
+        return add_rmsnorm_launch<__nv_bfloat16, __nv_bfloat16>(resid, delta, weight, out, rows,
+                                                                 n_rows, hidden, eps, s);
+    if (delta_dtype == RV_DTYPE_F32 && out_dtype == RV_DTYPE_BF16)
+        return add_rmsnorm_launch<float, __nv_bfloat16>(resid, delta, weight, out, rows, n_rows,
+                                                        hidden, eps, s);
+    if (delta_dtype == RV_DTYPE_BF16 && out_dtype == RV_DTYPE_F32)
+        return add_rmsnorm_launch<__nv_bfloat16, float>(resid, delta, weight, out, rows, n_rows,
+                                                        hidden, eps, s);
+    RV_FAIL("add_rmsnorm: unknown dtype codes %d, %d", delta_dtype, out_dtype);
+}
+
+// ---------------------------------------------------------------------------------
+// SwiGLU activation: out[n, f] = silu(in[n, f]) * in[n, F + f], silu(z) = z / (1 + e^-z).
+// Reference counterpart: silu_gate_multiply.cu (two separate inputs).
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ in, T* __restrict__ out, int ffn, size_t total) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (size_t)gridDim.x * blockDim.x) {
+        const size_t n = i / ffn;
+        const int f = (int)(i - n * ffn);
+        const float g = rv_load(in + n * 2 * ffn + f);
+        const float u = rv_load(in + n * 2 * ffn + ffn + f);
+        rv_store(out + i, g / (1.f + __expf(-g)) * u);
+    }
+}
+
+// bfloat16, 8 elements per thread (16-byte loads); needs ffn % 8 == 0.
+__global__ void swiglu_bf16x8_kernel(const uint4* __restrict__ in, uint4* __restrict__ out,
+                                     int ffn8, size_t total8) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total8;
+         i += (size_t)gridDim.x * blockDim.x) {
+        const size_t n = i / ffn8;
+        const int f = (int)(i - n * ffn8);
+        uint4 g4 = in[n * 2 * ffn8 + f], u4 = in[n * 2 * ffn8 + ffn8 + f], o4;
+        const __nv_bfloat162* g2 = (const __nv_bfloat162*)&g4;
+        const __nv_bfloat162* u2 = (const __nv_bfloat162*)&u4;
+        __nv_bfloat162* o2 = (__nv_bfloat162*)&o4;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float2 g = __bfloat1622float2(g2[k]), u = __bfloat1622float2(u2[k]);
+            o2[k] = __floats2bfloat162_rn(g.x / (1.f + __expf(-g.x)) * u.x,
+                                          g.y / (1.f + __expf(-g.y)) * u.y);
+        }
+        out[i] = o4;
+    }
+}
+
+extern "C" int rv_swiglu(const void* in, void* out, int dtype, int n_rows, int ffn, void* stream) {
+    if (n_rows == 0) return 0;
+    if (n_rows < 0 || ffn <= 0) RV_FAIL("swiglu: bad sizes");
+    const size_t total = (size_t)n_rows * ffn;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == RV_DTYPE_BF16 && ffn % 8 == 0 && ((uintptr_t)in % 16 == 0) &&
+        ((uintptr_t)out % 16 == 0)) {
+        const size_t total8 = total / 8;
+        const int blocks = (int)((total8 + 255) / 256 < 148 * 16 ? (total8 + 255) / 256 : 148 * 16);
+        swiglu_bf16x8_kernel<<<blocks, 256, 0, s>>>((const uint4*)in, (uint4*)out, ffn / 8, total8);
+    } else {
+        const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+        RV_DISPATCH_DTYPE(dtype, "swiglu",
+                          (swiglu_kernel<T><<<blocks, 256, 0, s>>>((const T*)in, (T*)out, ffn, total)));
+    }
+    RV_CHECK_LAUNCH("swiglu");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------
+// x[n, :] += bias (float32 bias).  Reference counterpart: add_bias.cu.
+template <typename T>
+__global__ void add_bias_kernel(T* __restrict__ x, const float* __restrict__ bias, int width,
+                                size_t total) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (size_t)gridDim.x * blockDim.x)
+        rv_store(x + i, rv_load(x + i) + bias[i % width]);
+}
+
+extern "C" int rv_add_bias(void* x, int dtype, const float* bias, int n_rows, int width,
+                           void* stream) {
+    if (n_rows == 0) return 0;
+    if (n_rows < 0 || width <= 0) RV_FAIL("add_bias: bad sizes");
+    const size_t total = (size_t)n_rows * width;
+    const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    RV_DISPATCH_DTYPE(dtype, "add_bias",
+                      (add_bias_kernel<T><<<blocks, 256, 0, (cudaStream_t)stream>>>(
+                          (T*)x, bias, width, total)));
+    RV_CHECK_LAUNCH("add_bias");
+    return 0;
+}

@@ -1,0 +1,136 @@
+// Gated short convolution for any mixture of prompt portions and single tokens:
+// gate B*x, load of the request's state, the causal taps, gate C, and the store of the
+// new state, in one kernel.
+//
+//   proj[t] = (B | C | x), three chunks of `hidden` channels (plus the optional bias)
+//   bx[t]   = B[t] * x[t]
+//   window  = the request's taps-1 previous bx rows (the state; zeros before position
+//             0), then this step's bx rows
+//   out[t]  = C[t] * (sum_k filter[c, k] * window[t + k] + conv_bias[c])
+//   state'  = the window's last taps-1 rows
+//
+// One thread owns one channel of one chunk of 32 consecutive tokens of one request and
+// slides the window through registers.  The thread of chunk 0 is the only one that
+// reads or writes the state of its (request, channel): it reads the old rows before
+// anything else and writes the new rows last, so no other thread can see a half-updated
+// state.  Later chunks rebuild their first taps-1 window rows from proj.  The state is
+// float32 whatever the storage type, so a bx value is the same number whether it comes
+// from the state or is recomputed from proj.
+//
+// Reference counterparts: short_conv_bx and short_conv_filter_gate (short_conv.cu) with
+// per-item device-to-device copies around them (src/cuda/model.rs:599-677,
+// src/cuda/conv_cache.rs:61-115).  Plain reference: tests/plain_ops.py short_conv.
+#include "common.cuh"
+
+#define RV_CONV_MAX_TAPS 8
+#define RV_CONV_CHUNK 32
+
+template <typename T>
+__global__ void short_conv_kernel(const T* __restrict__ proj, const float* __restrict__ filter,
+                                  const float* __restrict__ in_bias,
+                                  const float* __restrict__ conv_bias, float* __restrict__ state,
+                                  const int* __restrict__ q_start, const int* __restrict__ state_slot,
+                                  const int* __restrict__ start_pos, T* __restrict__ out,
+                                  int hidden, int taps) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= hidden) return;
+    const int r = blockIdx.y;
+    const int q0 = q_start[r];
+    const int qlen = q_start[r + 1] - q0;
+    const int t0 = blockIdx.z * RV_CONV_CHUNK;
+    if (t0 >= qlen) return;
+    const int slot = state_slot[r];
+    const int hist = taps - 1;
+    const bool has_state = slot >= 0 && start_pos[r] > 0 && hist > 0;
+    float* st = slot >= 0 ? state + (size_t)slot * hist * hidden + c : nullptr;
+
+    float f[RV_CONV_MAX_TAPS];
+#pragma unroll
+    for (int k = 0; k < RV_CONV_MAX_TAPS; ++k) f[k] = k < taps ? filter[(size_t)c * taps + k] : 0.f;
+    const float bb = in_bias ? in_bias[c] : 0.f;
+    const float bc = in_bias ? in_bias[hidden + c] : 0.f;
+    const float bxb = in_bias ? in_bias[2 * hidden + c] : 0.f;
+    const float cb = conv_bias ? conv_bias[c] : 0.f;
+    const size_t stride = (size_t)3 * hidden;
+
+    auto bx_at = [&](int rel) -> float {   // B*x of the request's rel-th token of this step
+        const T* p = proj + (size_t)(q0 + rel) * stride + c;
+        return (rv_load(p) + bb) * (rv_load(p + 2 * hidden) + bxb);
+    };
+
+    // window rows before token t0; in chunk 0 they are the old state
+    float old[RV_CONV_MAX_TAPS - 1];
+    float win[RV_CONV_MAX_TAPS - 1];
+#pragma unroll
+    for (int i = 0; i < RV_CONV_MAX_TAPS - 1; ++i) {
+        old[i] = 0.f;
+        win[i] = 0.f;
+        if (i < hist) {
+            const int rel = t0 - hist + i;
+            if (rel >= 0) {
+                win[i] = bx_at(rel);
+            } else if (has_state) {
+                old[i] = st[(size_t)(hist + rel) * hidden];
+                win[i] = old[i];
+            }
+        }
+    }
+    const int t1 = min(t0 + RV_CONV_CHUNK, qlen);
+    for (int t = t0; t < t1; ++t) {
+        const T* p = proj + (size_t)(q0 + t) * stride + c;
+        const float bx = (rv_load(p) + bb) * (rv_load(p + 2 * hidden) + bxb);
+        const float gate_c = rv_load(p + hidden) + bc;
+        float acc = 0.f;
+#pragma unroll
+        for (int k = 0; k < RV_CONV_MAX_TAPS - 1; ++k)
+            if (k < hist) acc += f[k] * win[k];
+        acc += f[hist] * bx;
+        rv_store(out + (size_t)(q0 + t) * hidden + c, gate_c * (acc + cb));
+#pragma unroll
+        for (int k = 0; k < RV_CONV_MAX_TAPS - 2; ++k)
+            if (k + 1 < hist) win[k] = win[k + 1];
+        if (hist > 0) {
+#pragma unroll
+            for (int k = 0; k < RV_CONV_MAX_TAPS - 1; ++k)
+                if (k == hist - 1) win[k] = bx;
+        }
+    }
+    if (t0 == 0 && st && hist > 0) {
+        // new state row i = window row qlen + i; window row w < hist is old[w]
+#pragma unroll
+        for (int i = 0; i < RV_CONV_MAX_TAPS - 1; ++i) {
+            if (i < hist) {
+                const int w = qlen + i;
+                float v = 0.f;
+                if (w >= hist) {
+                    v = bx_at(w - hist);
+                } else {
+#pragma unroll
+                    for (int k = 0; k < RV_CONV_MAX_TAPS - 1; ++k)
+                        if (k == w) v = old[k];
+                }
+                st[(size_t)i * hidden] = v;
+            }
+        }
+    }
+}
+
+extern "C" int rv_short_conv(const void* proj, int dtype, const float* filter, const float* in_bias,
+                             const float* conv_bias, float* state, const int* q_start,
+                             const int* state_slot, const int* start_pos, void* out, int n_reqs,
+                             int max_q_len, int hidden, int taps, void* stream) {
+    if (n_reqs == 0) return 0;
+    if (n_reqs < 0 || hidden <= 0 || max_q_len <= 0) RV_FAIL("short_conv: bad sizes");
+    if (taps < 1 || taps > RV_CONV_MAX_TAPS)
+        RV_FAIL("short_conv: filter length %d is not supported (1 to %d)", taps, RV_CONV_MAX_TAPS);
+    if (taps > 1 && !state) RV_FAIL("short_conv: a filter of length %d needs a state", taps);
+    const int chunks = (max_q_len + RV_CONV_CHUNK - 1) / RV_CONV_CHUNK;
+    if (n_reqs > 65535 || chunks > 65535) RV_FAIL("short_conv: batch too large for one launch");
+    dim3 grid((hidden + 127) / 128, n_reqs, chunks);
+    RV_DISPATCH_DTYPE(dtype, "short_conv",
+                      (short_conv_kernel<T><<<grid, 128, 0, (cudaStream_t)stream>>>(
+                          (const T*)proj, filter, in_bias, conv_bias, state, q_start, state_slot,
+                          start_pos, (T*)out, hidden, taps)));
+    RV_CHECK_LAUNCH("short_conv");
+    return 0;
+}

@@ -1,0 +1,261 @@
+"""The CUDA kernel set: ctypes bindings of the native library, with the interface the
+parts call (`embed`, `add_rmsnorm`, `linear`, `qk_norm_rope_write`, `paged_attention`,
+`short_conv`, `swiglu`, `add_bias`, `argmax`, `sample`).
+
+Every kernel launches on torch's current stream, so captured graphs and ordinary
+stream order both work.  Matrix products go to cuBLAS through `torch.mm`, as the
+reference sends them to cuBLAS (src/cuda/cublas_ops.rs:44-92); with float32 operands
+TF32 is switched off, so the float32 path is float32 throughout.  There is no CPU
+path here: constructing `CudaOps` without a CUDA device or without the library raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+import torch
+
+from ..errors import KernelError
+from .build import build
+
+_F32, _BF16 = 0, 1
+
+
+def _code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return _F32
+    if dtype == torch.bfloat16:
+        return _BF16
+    raise KernelError(f"kernels take float32 or bfloat16 tensors, got {dtype}")
+
+
+def _ptr(t):
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+class CudaOps:
+    name = "cuda"
+
+    def __init__(self, verbose_build: bool = True):
+        if not torch.cuda.is_available():
+            raise KernelError("rvllm_b200 needs a CUDA device: there is no CPU path")
+        path = build(verbose=verbose_build)
+        try:
+            self.lib = ctypes.CDLL(path)
+        except OSError as e:
+            raise KernelError(f"cannot load the kernel library {path}: {e}") from None
+        self.library_path = path
+        self.lib.rv_last_error.restype = ctypes.c_char_p
+        self.lib.rv_paged_attention_decode_scratch_bytes.restype = c_longlong
+        self._scratch = {}
+        # float32 products must be float32: no TF32, no reduced-precision accumulation
+        torch.backends.cuda.matmul.allow_tf32 = False
+        torch.backends.cudnn.allow_tf32 = False
+        torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
+        self.launches = 0
+
+    # ---- plumbing --------------------------------------------------------------------
+
+    def _check(self, rc: int, what: str) -> None:
+        self.launches += 1
+        if rc != 0:
+            raise KernelError(f"{what}: {self.lib.rv_last_error().decode()}")
+
+    @staticmethod
+    def _stream() -> c_void_p:
+        return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    @staticmethod
+    def _need(t: torch.Tensor, what: str, dtype=None, contiguous=True):
+        if not t.is_cuda:
+            raise KernelError(f"{what} must be a CUDA tensor")
+        if contiguous and not t.is_contiguous():
+            raise KernelError(f"{what} must be contiguous")
+        if dtype is not None and t.dtype != dtype:
+            raise KernelError(f"{what} must be {dtype}, got {t.dtype}")
+
+    # ---- embedding -------------------------------------------------------------------
+
+    def embed(self, table, ids, out, scale=None):
+        self._need(table, "embedding table")
+        self._need(ids, "token ids", torch.int32)
+        self._need(out, "embedding output", torch.float32)
+        n, hidden = out.shape
+        self._check(self.lib.rv_embed(_ptr(table), _code(table.dtype), _ptr(ids), _ptr(out),
+                                      c_int(n), c_int(hidden), c_int(table.shape[0]),
+                                      c_float(1.0 if scale is None else scale), self._stream()),
+                    "embed")
+
+    # ---- residual add + RMSNorm ------------------------------------------------------
+
+    def add_rmsnorm(self, resid, delta, weight, eps, out, rows=None):
+        self._need(resid, "residual stream", torch.float32)
+        self._need(weight, "norm weight", torch.float32)
+        self._need(out, "norm output")
+        if delta is not None:
+            self._need(delta, "pending sub-layer output")
+            if delta.shape != resid.shape:
+                raise KernelError("add_rmsnorm: the stream and the pending output differ in shape")
+        if rows is not None:
+            self._need(rows, "row list", torch.int32)
+        n, hidden = out.shape
+        if resid.shape[1] != hidden or weight.shape[0] != hidden:
+            raise KernelError("add_rmsnorm: widths disagree")
+        self._check(self.lib.rv_add_rmsnorm(
+            _ptr(resid), _ptr(delta), _code(delta.dtype) if delta is not None else _F32,
+            _ptr(weight), _ptr(out), _code(out.dtype), _ptr(rows), c_int(n), c_int(hidden),
+            c_float(eps), self._stream()), "add_rmsnorm")
+
+    # ---- matrix product (library) -------------------------------------------------------
+
+    def linear(self, x, w, bias=None, out_dtype=None):
+        out_dtype = out_dtype or x.dtype
+        if x.dtype != w.dtype:
+            # a matrix kept in 32 bits is multiplied in 32 bits
+            wide = torch.float32 if torch.float32 in (x.dtype, w.dtype) else x.dtype
+            x, w = x.to(wide), w.to(wide)
+        if x.shape[0] == 0:
+            return torch.empty((0, w.shape[0]), dtype=out_dtype, device=x.device)
+        if out_dtype == x.dtype:
+            y = torch.mm(x, w.t())
+        elif x.dtype == torch.bfloat16 and out_dtype == torch.float32:
+            y = torch.mm(x, w.t(), out_dtype=torch.float32)
+        else:
+            y = torch.mm(x, w.t()).to(out_dtype)
+        if bias is not None:
+            self.add_bias(y, bias)
+        return y
+
+    def add_bias(self, x, bias):
+        self._need(x, "add_bias input")
+        self._need(bias, "bias", torch.float32)
+        self._check(self.lib.rv_add_bias(_ptr(x), _code(x.dtype), _ptr(bias), c_int(x.shape[0]),
+                                         c_int(x.shape[1]), self._stream()), "add_bias")
+
+    # ---- q/k norm + rotation + cache write -------------------------------------------
+
+    def qk_norm_rope_write(self, qkv, num_heads, num_kv_heads, head_dim, q_weight, k_weight,
+                           eps, table, positions, slot_mapping, k_cache, v_cache):
+        self._need(qkv, "q|k|v rows")
+        if qkv.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim:
+            raise KernelError("qk_norm_rope_write: row width and head counts disagree")
+        if k_cache is not None:
+            self._need(k_cache, "key pages", qkv.dtype)
+            self._need(v_cache, "value pages", qkv.dtype)
+        cos, sin = table if table is not None else (None, None)
+        self._check(self.lib.rv_qk_norm_rope_write(
+            _ptr(qkv), _code(qkv.dtype), c_int(qkv.shape[1]), c_int(qkv.shape[0]),
+            c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), _ptr(q_weight),
+            _ptr(k_weight), c_float(eps), _ptr(cos), _ptr(sin), _ptr(positions),
+            _ptr(slot_mapping), _ptr(k_cache), _ptr(v_cache), self._stream()),
+            "qk_norm_rope_write")
+
+    # ---- attention -------------------------------------------------------------------
+
+    def _scratch_buffer(self, nbytes: int, device) -> torch.Tensor:
+        buf = self._scratch.get(device)
+        if buf is None or buf.numel() < nbytes:
+            buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+            self._scratch[device] = buf
+        return buf
+
+    def paged_attention(self, qkv, num_heads, num_kv_heads, head_dim, k_cache, v_cache,
+                        ctx, group, scale, window, out):
+        self._need(qkv, "query rows")
+        self._need(out, "attention output", qkv.dtype)
+        self._need(k_cache, "key pages", qkv.dtype)
+        self._need(v_cache, "value pages", qkv.dtype)
+        code = _code(qkv.dtype)
+        win = c_int(window if window else 0)
+        nd = ctx.n_decode
+        if nd > 0:
+            self.paged_attention_decode(qkv, num_heads, num_kv_heads, head_dim, k_cache, v_cache,
+                                        group.block_table, ctx.ctx_lens, nd, ctx.max_ctx_len,
+                                        group.page_size, scale, window, out)
+        if ctx.n_tokens > nd:
+            self._check(self.lib.rv_paged_attention_warp(
+                _ptr(qkv), code, c_int(qkv.shape[1]), _ptr(k_cache), _ptr(v_cache),
+                _ptr(group.block_table), c_int(group.max_blocks), _ptr(ctx.q_start),
+                _ptr(ctx.ctx_lens), _ptr(ctx.token_req), _ptr(out), c_int(nd),
+                c_int(ctx.n_tokens - nd), c_int(num_heads), c_int(num_kv_heads),
+                c_int(head_dim), c_int(group.page_size), c_float(scale), win,
+                self._stream()), "paged_attention")
+
+    def paged_attention_decode(self, qkv, num_heads, num_kv_heads, head_dim, k_cache, v_cache,
+                               block_table, ctx_lens, n_reqs, max_ctx_len, page_size, scale,
+                               window, out, scratch=None):
+        """Split-KV attention for requests [0, n_reqs) that bring one token each."""
+        need = self.lib.rv_paged_attention_decode_scratch_bytes(
+            c_int(n_reqs), c_int(num_heads), c_int(head_dim), c_int(max_ctx_len))
+        if scratch is None:
+            scratch = self._scratch_buffer(need, qkv.device)
+        self._check(self.lib.rv_paged_attention_decode(
+            _ptr(qkv), _code(qkv.dtype), c_int(qkv.shape[1]), _ptr(k_cache), _ptr(v_cache),
+            _ptr(block_table), c_int(block_table.shape[1]), _ptr(ctx_lens), _ptr(out),
+            _ptr(scratch), c_longlong(scratch.numel() * scratch.element_size()),
+            c_int(n_reqs), c_int(max_ctx_len), c_int(num_heads), c_int(num_kv_heads),
+            c_int(head_dim), c_int(page_size), c_float(scale), c_int(window if window else 0),
+            self._stream()), "paged_attention_decode")
+
+    def paged_attention_general(self, qkv, num_heads, num_kv_heads, head_dim, k_cache, v_cache,
+                                ctx, group, scale, window, out):
+        """Every token through the one-warp-per-(token, head) kernel."""
+        self._check(self.lib.rv_paged_attention_warp(
+            _ptr(qkv), _code(qkv.dtype), c_int(qkv.shape[1]), _ptr(k_cache), _ptr(v_cache),
+            _ptr(group.block_table), c_int(group.max_blocks), _ptr(ctx.q_start),
+            _ptr(ctx.ctx_lens), _ptr(ctx.token_req), _ptr(out), c_int(0), c_int(ctx.n_tokens),
+            c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(group.page_size),
+            c_float(scale), c_int(window if window else 0), self._stream()), "paged_attention")
+
+    # ---- gated short convolution -----------------------------------------------------
+
+    def short_conv(self, proj, filt, in_bias, conv_bias, state, ctx, out):
+        self._need(proj, "in_proj rows")
+        self._need(filt, "filter", torch.float32)
+        self._need(out, "short_conv output", proj.dtype)
+        hidden, taps = filt.shape
+        if proj.shape[1] != 3 * hidden:
+            raise KernelError("short_conv: in_proj rows must be three times the filter's width")
+        if state is not None:
+            self._need(state, "convolution state", torch.float32)
+        self._check(self.lib.rv_short_conv(
+            _ptr(proj), _code(proj.dtype), _ptr(filt), _ptr(in_bias), _ptr(conv_bias),
+            _ptr(state), _ptr(ctx.q_start), _ptr(ctx.state_slot), _ptr(ctx.start_pos), _ptr(out),
+            c_int(ctx.n_reqs), c_int(ctx.max_q_len), c_int(hidden), c_int(taps),
+            self._stream()), "short_conv")
+
+    # ---- SwiGLU ----------------------------------------------------------------------
+
+    def swiglu(self, gate_up, out):
+        self._need(gate_up, "gate|up rows")
+        self._need(out, "swiglu output", gate_up.dtype)
+        if gate_up.shape[1] != 2 * out.shape[1]:
+            raise KernelError("swiglu: input rows must be twice the output's width")
+        self._check(self.lib.rv_swiglu(_ptr(gate_up), _ptr(out), _code(out.dtype),
+                                       c_int(out.shape[0]), c_int(out.shape[1]), self._stream()),
+                    "swiglu")
+
+    # ---- sampling --------------------------------------------------------------------
+
+    def argmax(self, logits):
+        self._need(logits, "logits", torch.float32)
+        out = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
+        self._check(self.lib.rv_argmax(_ptr(logits), _ptr(out), c_int(logits.shape[0]),
+                                       c_int(logits.shape[1]), self._stream()), "argmax")
+        return out
+
+    def sample(self, logits, temperature, top_p, seed, counter):
+        """Rows with temperature <= 0 are greedy."""
+        self._need(logits, "logits", torch.float32)
+        self._need(temperature, "temperatures", torch.float32)
+        self._need(top_p, "top-p values", torch.float32)
+        self._need(seed, "seeds", torch.int64)
+        self._need(counter, "counters", torch.int64)
+        greedy = self.argmax(logits)
+        out = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
+        positive = temperature.clamp_min(1e-6)
+        self._check(self.lib.rv_sample(_ptr(logits), _ptr(positive),
+                                       _ptr(top_p), _ptr(seed), _ptr(counter), _ptr(out),
+                                       c_int(logits.shape[0]), c_int(logits.shape[1]),
+                                       self._stream()), "sample")
+        return torch.where(temperature > 0, out, greedy)

@@ -1,0 +1,2 @@
+from .params import GREEDY, SamplingParams
+from .sampler import BatchSampler

@@ -1,0 +1,145 @@
+"""The engine on the GPU against the plain implementation, in float32 and in bfloat16:
+each request alone and whole; most of it in one step and the last 32 tokens one by one;
+portions of changing size; mixed batches with few pages; long decoding; first tokens."""
+import random
+
+import pytest
+import torch
+
+import schedules
+from plain_lfm2 import PlainModel
+from tiny import write_tiny
+
+pytestmark = pytest.mark.gpu
+
+# float32: the engine and the plain implementation differ by float32 rounding only.
+# bfloat16: weights are the same numbers (the files store bfloat16), activations are
+# rounded to 8 bits of mantissa (relative 2^-9) at about ten places per layer; over the
+# tiny models' 4 to 6 layers this stays below 3 % of the largest logit.
+BOUND = {"float32": 1e-5, "bfloat16": 3e-2}
+
+
+def _requests(vocab, lengths, seed):
+    rng = random.Random(seed)
+    return {f"r{i}": [rng.randrange(vocab) for _ in range(n)] for i, n in enumerate(lengths)}
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    root = str(tmp_path_factory.mktemp("models"))
+    return {n: write_tiny(root, n) for n in ("A", "B")}
+
+
+@pytest.fixture(scope="module")
+def plains(folders):
+    return {n: PlainModel(f) for n, f in folders.items()}
+
+
+_models = {}
+
+
+def engine(folders, name, dtype):
+    from rvllm_b200.engine import load_model
+    key = (name, dtype)
+    if key not in _models:
+        _models[key] = load_model(folders[name], dtype, "cuda")
+    return _models[key]
+
+
+def runner_for(model, page, pages, slots=4, graphs=False):
+    from rvllm_b200.engine import ModelRunner, make_cache
+    cache = make_cache(model, page, pages, slots)
+    return ModelRunner(model, cache, model.ops, use_graphs=graphs)
+
+
+def compare(got, plain, reqs, dtype):
+    worst = 0.0
+    for rid, ids in reqs.items():
+        ref = plain.logits(ids)
+        scale = float(ref.abs().max())
+        for p in range(len(ids)):
+            err = float((got[(rid, p)] - ref[p]).abs().max()) / scale
+            worst = max(worst, err)
+            assert err <= BOUND[dtype], (rid, p, err)
+            if dtype == "float32":
+                assert int(got[(rid, p)].argmax()) == int(ref[p].argmax()), (rid, p)
+    return worst
+
+
+LENGTHS = [5, 17, 31, 70, 9, 100, 64, 33]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("schedule", ["whole", "tail_decode", "portions", "mixed"])
+@pytest.mark.parametrize("graphs", [False, True])
+def test_schedules(folders, plains, name, dtype, schedule, graphs):
+    if graphs and schedule in ("whole", "portions"):
+        pytest.skip("no single-token steps in this schedule")
+    model, cfg = engine(folders, name, dtype)
+    reqs = _requests(cfg.vocab_size, LENGTHS, seed=5)
+    steps = getattr(schedules, schedule)(reqs)
+    page = 8 if name == "A" else 16
+    pages = schedules.tokens_held(steps, 64) // page
+    runner = runner_for(model, page, pages, graphs=graphs)
+    got = schedules.replay(runner, steps)
+    assert runner.cache.groups[0].pool.in_use == 0
+    compare(got, plains[name], reqs, dtype)
+    if schedule == "mixed":
+        pool = runner.cache.groups[0].pool
+        assert pool.total_allocs > pool.high_water       # pages were used again
+    if graphs:
+        assert runner.graph_steps > 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_cut_does_not_matter_float32(folders, plains, dtype):
+    """The same position computed under different cuts agrees far more closely than the
+    bound against the plain implementation."""
+    model, cfg = engine(folders, "B", dtype)
+    reqs = _requests(cfg.vocab_size, [90, 41], seed=8)
+    outs = []
+    for schedule in ("whole", "tail_decode", "portions", "mixed"):
+        steps = getattr(schedules, schedule)(reqs)
+        runner = runner_for(model, 16, schedules.tokens_held(steps, 64) // 16)
+        outs.append(schedules.replay(runner, steps))
+    bound = 2e-6 if dtype == "float32" else 2e-2
+    for key, row in outs[0].items():
+        for other in outs[1:]:
+            assert float((other[key] - row).abs().max()) <= bound * float(row.abs().max()), key
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_long_decode(folders, plains, name, dtype):
+    """A short prompt, then token by token up to the model's last position."""
+    model, cfg = engine(folders, name, dtype)
+    n = cfg.max_position_embeddings
+    reqs = _requests(cfg.vocab_size, [n], seed=9)
+    steps = schedules.tail_decode(reqs, tail=n - 3)
+    page = 16
+    runner = runner_for(model, page, -(-n // 64) * 64 // page, graphs=True)
+    got = schedules.replay(runner, steps)
+    compare(got, plains[name], reqs, dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_first_tokens(folders, plains, name, dtype):
+    """Prompts of one to five tokens: the first positions, where the convolution state
+    is all zeros and a page holds a single key."""
+    model, cfg = engine(folders, name, dtype)
+    reqs = _requests(cfg.vocab_size, [1, 2, 3, 4, 5], seed=10)
+    for fn in (schedules.whole, schedules.tail_decode, schedules.mixed):
+        steps = fn(reqs)
+        runner = runner_for(model, 16, schedules.tokens_held(steps, 64) // 16)
+        compare(schedules.replay(runner, steps), plains[name], reqs, dtype)
+
+
+def test_position_past_the_table_is_refused(folders):
+    model, cfg = engine(folders, "A", "float32")
+    from rvllm_b200.engine import StepEntry
+    runner = runner_for(model, 16, 32)
+    runner.add_request("x")
+    with pytest.raises(ValueError, match="exceed"):
+        runner.step([StepEntry("x", [1] * (cfg.max_position_embeddings + 1), [0])])

@@ -1,0 +1,305 @@
+"""Each CUDA kernel alone against its plain reference (tests/plain_ops.py), at sizes
+other than the engine's: widths that are no power of two, head sizes 48 and 80, groups
+of 3, pages of 8, filters of 2 to 5 taps."""
+import math
+import random
+from types import SimpleNamespace
+
+import pytest
+import torch
+
+from plain_ops import PlainOps, sample_row, uniform
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from rvllm_b200.kernels import cuda_ops
+    return cuda_ops()
+
+
+def tol(dtype):
+    return dict(atol=2e-6, rtol=2e-6) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+
+
+def rnd(shape, dtype, gen, scale=1.0):
+    return (torch.randn(shape, generator=gen) * scale).to(dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embed(ops, dtype):
+    g = torch.Generator().manual_seed(1)
+    table = rnd((777, 200), dtype, g)
+    ids = torch.randint(0, 777, (37,), generator=g, dtype=torch.int32)
+    ref = torch.empty(37, 200)
+    PlainOps().embed(table, ids, ref, 1.5)
+    out = torch.empty(37, 200, device="cuda")
+    ops.embed(table.cuda(), ids.cuda(), out, 1.5)
+    assert torch.equal(out.cpu(), ref)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden", [200, 1000, 2048])
+def test_add_rmsnorm(ops, dtype, hidden):
+    g = torch.Generator().manual_seed(2)
+    resid = rnd((19, hidden), torch.float32, g)
+    delta = rnd((19, hidden), dtype, g)
+    w = 1 + rnd((hidden,), torch.float32, g, 0.05)
+    for use_delta in (True, False):
+        r_ref, out_ref = resid.clone(), torch.empty(19, hidden, dtype=dtype)
+        PlainOps().add_rmsnorm(r_ref, delta if use_delta else None, w, 1e-5, out_ref)
+        r_gpu, out = resid.cuda(), torch.empty(19, hidden, dtype=dtype, device="cuda")
+        ops.add_rmsnorm(r_gpu, delta.cuda() if use_delta else None, w.cuda(), 1e-5, out)
+        assert torch.allclose(r_gpu.cpu(), r_ref, atol=1e-6, rtol=1e-6)
+        assert torch.allclose(out.cpu().float(), out_ref.float(), **tol(dtype))
+    rows = torch.tensor([3, 18, 0, 3], dtype=torch.int32)
+    out_ref = torch.empty(4, hidden, dtype=dtype)
+    PlainOps().add_rmsnorm(resid.clone(), delta, w, 1e-6, out_ref, rows)
+    r_gpu, out = resid.cuda(), torch.empty(4, hidden, dtype=dtype, device="cuda")
+    ops.add_rmsnorm(r_gpu, delta.cuda(), w.cuda(), 1e-6, out, rows.cuda())
+    assert torch.equal(r_gpu.cpu(), resid)          # stream untouched with a row list
+    assert torch.allclose(out.cpu().float(), out_ref.float(), **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("ffn", [200, 1024])
+def test_swiglu(ops, dtype, ffn):
+    g = torch.Generator().manual_seed(3)
+    x = rnd((13, 2 * ffn), dtype, g, 2.0)
+    ref = torch.empty(13, ffn, dtype=dtype)
+    PlainOps().swiglu(x, ref)
+    out = torch.empty(13, ffn, dtype=dtype, device="cuda")
+    ops.swiglu(x.cuda(), out)
+    assert torch.allclose(out.cpu().float(), ref.float(), **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_add_bias(ops, dtype):
+    g = torch.Generator().manual_seed(4)
+    x, b = rnd((11, 77), dtype, g), rnd((77,), torch.float32, g)
+    ref = x.clone()
+    PlainOps().add_bias(ref, b)
+    out = x.cuda()
+    ops.add_bias(out, b.cuda())
+    assert torch.allclose(out.cpu().float(), ref.float(), **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_linear_float32_is_float32(ops, dtype):
+    g = torch.Generator().manual_seed(5)
+    x, w = rnd((33, 300), dtype, g), rnd((70, 300), dtype, g)
+    ref = x.double() @ w.double().t()
+    out = ops.linear(x.cuda(), w.cuda(), out_dtype=torch.float32).cpu().double()
+    # float32 operands: errors of float32 accumulation only (TF32 would give ~1e-3)
+    bound = 2e-5 if dtype == torch.float32 else 2e-5
+    assert (out - ref).abs().max() <= bound * ref.abs().max()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("norm,rope", [(True, True), (False, True), (True, False)])
+def test_qk_norm_rope_write(ops, dtype, norm, rope):
+    g = torch.Generator().manual_seed(6)
+    nh, nkv, hd, n, ps, pages = 6, 2, 48, 21, 8, 9
+    qkv = rnd((n, (nh + 2 * nkv) * hd), dtype, g)
+    qw = (1 + rnd((hd,), torch.float32, g, 0.1)) if norm else None
+    kw = (1 + rnd((hd,), torch.float32, g, 0.1)) if norm else None
+    positions = torch.randint(0, 300, (n,), generator=g, dtype=torch.int32)
+    table = None
+    if rope:
+        ang = torch.arange(300).float().unsqueeze(1) * torch.pow(
+            torch.tensor(10000.0), -2.0 * torch.arange(hd // 2).float() / hd)
+        table = (ang.cos(), ang.sin())
+    slots = torch.randperm(pages * ps, generator=g)[:n].to(torch.int32)
+    slots[5] = -1
+    kc = rnd((pages, ps, nkv, hd), dtype, g)
+    vc = rnd((pages, ps, nkv, hd), dtype, g)
+    ref_qkv, ref_k, ref_v = qkv.clone(), kc.clone(), vc.clone()
+    PlainOps().qk_norm_rope_write(ref_qkv, nh, nkv, hd, qw, kw, 1e-6, table, positions, slots,
+                                  ref_k, ref_v)
+    d_qkv, d_k, d_v = qkv.cuda(), kc.cuda(), vc.cuda()
+    ops.qk_norm_rope_write(d_qkv, nh, nkv, hd, qw.cuda() if norm else None,
+                           kw.cuda() if norm else None, 1e-6,
+                           (table[0].cuda(), table[1].cuda()) if rope else None,
+                           positions.cuda(), slots.cuda(), d_k, d_v)
+    t = tol(dtype)
+    assert torch.allclose(d_qkv[:, :nh * hd].cpu().float(), ref_qkv[:, :nh * hd].float(), **t)
+    assert torch.allclose(d_k.cpu().float(), ref_k.float(), **t)
+    assert torch.equal(d_v.cpu(), ref_v)
+
+
+def attention_case(dtype, g, q_lens, ctx_lens, nh, nkv, hd, ps, window=None, standout=False):
+    """A batch with random pages in a shuffled pool.  With `standout`, one far key of
+    every request is made to dominate the softmax of its last query."""
+    R = len(q_lens)
+    n = sum(q_lens)
+    blocks = [-(-c // ps) for c in ctx_lens]
+    pages = sum(blocks) + 3
+    perm = torch.randperm(pages, generator=g).tolist()
+    mb = max(blocks)
+    table = torch.full((R, mb), -1, dtype=torch.int32)
+    k = 0
+    for r in range(R):
+        for b in range(blocks[r]):
+            table[r, b] = perm[k]
+            k += 1
+    kc = rnd((pages, ps, nkv, hd), dtype, g)
+    vc = rnd((pages, ps, nkv, hd), dtype, g)
+    q = rnd((n, (nh + 2 * nkv) * hd), dtype, g)
+    q_start = [0]
+    for ql in q_lens:
+        q_start.append(q_start[-1] + ql)
+    token_req = [r for r, ql in enumerate(q_lens) for _ in range(ql)]
+    if standout:
+        for r in range(R):
+            p = ctx_lens[r] - 1
+            lo = 0 if window is None else max(0, p - window + 1)
+            far = lo + (p - lo) // 7           # a key far from the query, inside the window
+            t_last = q_start[r + 1] - 1
+            page, slot = int(table[r, far // ps]), far % ps
+            for h in range(nh):
+                qh = q[t_last, h * hd:(h + 1) * hd].float()
+                kc[page, slot, h // (nh // nkv)] = (qh / qh.norm() * 6.0).to(dtype)
+    n_decode = 0
+    while n_decode < R and q_lens[n_decode] == 1:
+        n_decode += 1
+    ctx = SimpleNamespace(
+        n_tokens=n, n_reqs=R, n_decode=n_decode,
+        q_start=torch.tensor(q_start, dtype=torch.int32),
+        ctx_lens=torch.tensor(ctx_lens, dtype=torch.int32),
+        token_req=torch.tensor(token_req, dtype=torch.int32),
+        max_ctx_len=max(ctx_lens), max_q_len=max(q_lens))
+    group = SimpleNamespace(block_table=table, max_blocks=mb, page_size=ps, window=window)
+    return q, kc, vc, ctx, group
+
+
+def to_cuda(ns):
+    return SimpleNamespace(**{k: (v.cuda() if torch.is_tensor(v) else v)
+                              for k, v in vars(ns).items()})
+
+
+ATTN_CASES = [
+    # q_lens, ctx_lens, heads, kv heads, head size, page, window
+    ([1, 1, 5, 40], [1, 300, 5, 333], 6, 2, 48, 8, None),
+    ([1, 7, 2, 64], [700, 7, 130, 64], 3, 1, 80, 16, None),
+    ([1, 1, 9, 33], [290, 17, 100, 260], 8, 2, 16, 16, 37),
+    ([3], [515], 4, 4, 128, 32, None),
+]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("case", ATTN_CASES)
+@pytest.mark.parametrize("standout", [False, True])
+def test_paged_attention(ops, dtype, case, standout):
+    q_lens, ctx_lens, nh, nkv, hd, ps, window = case
+    g = torch.Generator().manual_seed(7)
+    q, kc, vc, ctx, group = attention_case(dtype, g, q_lens, ctx_lens, nh, nkv, hd, ps, window,
+                                           standout)
+    scale = 1.0 / math.sqrt(hd)
+    ref = torch.zeros(ctx.n_tokens, nh * hd, dtype=dtype)
+    PlainOps().paged_attention(q, nh, nkv, hd, kc, vc, ctx, group, scale, window, ref)
+    dq, dk, dv, dctx, dgroup = q.cuda(), kc.cuda(), vc.cuda(), to_cuda(ctx), to_cuda(group)
+    t = dict(atol=3e-6, rtol=1e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+    # the dispatching entry (decode kernel for single tokens, prefill kernel for the rest)
+    out = torch.full((ctx.n_tokens, nh * hd), float("nan"), dtype=dtype, device="cuda")
+    ops.paged_attention(dq, nh, nkv, hd, dk, dv, dctx, dgroup, scale, window, out)
+    assert torch.allclose(out.cpu().float(), ref.float(), **t)
+    # every token through the general kernel
+    out2 = torch.full((ctx.n_tokens, nh * hd), float("nan"), dtype=dtype, device="cuda")
+    ops.paged_attention_general(dq, nh, nkv, hd, dk, dv, dctx, dgroup, scale, window, out2)
+    assert torch.allclose(out2.cpu().float(), ref.float(), **t)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_paged_attention_padding_rows(ops, dtype):
+    """Requests with context 0 are padding: zeros out, nothing read."""
+    g = torch.Generator().manual_seed(8)
+    q, kc, vc, ctx, group = attention_case(dtype, g, [1, 1, 1], [40, 9, 300], 4, 2, 32, 16)
+    ctx.ctx_lens[1] = 0
+    group.block_table[1] = -1
+    out = torch.full((3, 4 * 32), float("nan"), dtype=dtype, device="cuda")
+    ops.paged_attention(q.cuda(), 4, 2, 32, kc.cuda(), vc.cuda(), to_cuda(ctx), to_cuda(group),
+                        0.17, None, out)
+    assert torch.all(out[1] == 0) and torch.isfinite(out).all()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("taps,bias", [(3, False), (4, True), (2, True), (5, False), (1, False)])
+def test_short_conv(ops, dtype, taps, bias):
+    g = torch.Generator().manual_seed(9)
+    hidden = 200
+    q_lens = [1, 1, 2, 5, 40, 70, 3]
+    start = [0, 9, 0, 4, 0, 33, 1]
+    slots = [5, 2, 7, 0, 3, 6, -1]
+    n = sum(q_lens)
+    proj = rnd((n, 3 * hidden), dtype, g)
+    filt = rnd((hidden, taps), torch.float32, g, 0.5)
+    b_in = rnd((3 * hidden,), torch.float32, g, 0.1) if bias else None
+    b_conv = rnd((hidden,), torch.float32, g, 0.1) if bias else None
+    state = rnd((8, max(taps - 1, 1), hidden), torch.float32, g)[:, :taps - 1].contiguous()
+    q_start = [0]
+    for ql in q_lens:
+        q_start.append(q_start[-1] + ql)
+    ctx = SimpleNamespace(n_reqs=len(q_lens), max_q_len=max(q_lens),
+                          q_start=torch.tensor(q_start, dtype=torch.int32),
+                          state_slot=torch.tensor(slots, dtype=torch.int32),
+                          start_pos=torch.tensor(start, dtype=torch.int32))
+    ref, ref_state = torch.empty(n, hidden, dtype=dtype), state.clone()
+    PlainOps().short_conv(proj, filt, b_in, b_conv, ref_state if taps > 1 else None, ctx, ref)
+    out, d_state = torch.empty(n, hidden, dtype=dtype, device="cuda"), state.cuda()
+    ops.short_conv(proj.cuda(), filt.cuda(), b_in.cuda() if bias else None,
+                   b_conv.cuda() if bias else None, d_state if taps > 1 else None,
+                   to_cuda(ctx), out)
+    assert torch.allclose(out.cpu().float(), ref.float(), **tol(dtype))
+    if taps > 1:
+        assert torch.allclose(d_state.cpu(), ref_state, atol=1e-6, rtol=1e-6)
+
+
+def test_argmax_first_maximum_and_nan(ops):
+    x = torch.randn(5, 1003)
+    x[0, 17] = x[0, 900] = 9.0                 # tie: the first wins
+    x[1, :] = float("-inf")                    # nothing above -inf: 0
+    x[2, 3] = float("nan")
+    x[2, 500] = 8.0
+    x[3, 1002] = 50.0                          # the last element of a ragged row
+    ref = PlainOps().argmax(x)
+    out = ops.argmax(x.cuda()).cpu()
+    assert out.tolist() == ref.tolist()
+    assert out[0] == 17 and out[1] == 0 and out[2] == 500 and out[3] == 1002
+
+
+@pytest.mark.parametrize("top_p", [1.0, 0.9, 0.3])
+def test_sample_matches_definition(ops, top_p):
+    g = torch.Generator().manual_seed(11)
+    vocab, rows = 1003, 64
+    logits = torch.randn(rows, vocab, generator=g) * 3
+    temp = torch.full((rows,), 0.8)
+    temp[5] = 0.0                               # a greedy row among sampled ones
+    tp = torch.full((rows,), top_p)
+    seed = torch.arange(rows, dtype=torch.int64) * 7 + 3
+    counter = torch.arange(rows, dtype=torch.int64)
+    out = ops.sample(logits.cuda(), temp.cuda(), tp.cuda(), seed.cuda(), counter.cuda()).cpu()
+    differ = []
+    for m in range(rows):
+        want = sample_row(logits[m], float(temp[m]), top_p, int(seed[m]), int(counter[m]))
+        if int(out[m]) != want:
+            differ.append((m, int(out[m]), want))
+    # float32 sums against the definition's float64 sums can move a draw that falls
+    # within rounding of a boundary to the neighbouring token; that is rare
+    assert len(differ) <= 1, differ
+    assert int(out[5]) == int(torch.argmax(logits[5]))
+
+
+def test_sample_frequencies(ops):
+    """Draws over many counters follow softmax(logits / T)."""
+    logits = torch.tensor([[2.0, 1.0, 0.0, -1.0, 0.5]])
+    n = 4000
+    L = logits.repeat(n, 1).cuda()
+    out = ops.sample(L, torch.full((n,), 0.7).cuda(), torch.ones(n).cuda(),
+                     torch.full((n,), 1234, dtype=torch.int64).cuda(),
+                     torch.arange(n, dtype=torch.int64).cuda()).cpu()
+    freq = torch.bincount(out.long(), minlength=5).double() / n
+    p = torch.softmax(logits[0].double() / 0.7, 0)
+    assert (freq - p).abs().max() < 0.03
