@@ -1,0 +1,307 @@
+"""Throughput of the LFM2 engine on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+A step is one decode step.  The default run uses the layer sizes of LFM2-1.2B (16
+layers: 10 gated short-convolution, 6 attention at [2,5,8,10,12,14]; hidden 2048; 32
+query heads, 8 KV heads, head size 64; feed-forward 12288 adjusted to 8192; filter
+length 3; vocabulary 65536; tied head) with random bfloat16 weights, a batch of 8 and
+a context of 4,096 tokens: every request is prefilled so that after the W warm-up
+steps it holds 4096 - K tokens, then K steps are timed with CUDA events and end at
+4,096.  The one JSON line printed holds
+
+  value      decoded tokens a second over the K timed steps, tokens fed back on the
+             device (no host round trip inside the timed region)
+  e2e        the same through the Python entry point (`Engine.step`): every step copies
+             its index arrays from pinned host memory and reads the sampled ids back
+  prefill    one step over a 2,048-token prompt: tokens a second, and its FLOPs / time /
+             the bfloat16 peak
+  roofline   the decode step's bytes (every weight once, the live requests' keys and
+             values and convolution states) / its time, against the HBM peak
+  points     decoded tokens a second at batch 1 and batch 64 (context 2,048 + steps)
+
+Peaks come from MEASURED_PEAKS.json beside this file when it exists ("of measured"),
+else from the fallback figures 6.65 TB/s and 1.59 PFLOP/s ("of fallback").
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+LFM2_1_2B = {
+    "architectures": ["Lfm2ForCausalLM"],
+    "num_hidden_layers": 16, "full_attn_idxs": [2, 5, 8, 10, 12, 14],
+    "hidden_size": 2048, "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 64,
+    "block_ff_dim": 12288, "block_auto_adjust_ff_dim": True, "block_multiple_of": 256,
+    "conv_L_cache": 3, "conv_bias": False, "vocab_size": 65536, "rope_theta": 1000000.0,
+    "max_position_embeddings": 4096, "norm_eps": 1e-5, "tie_embedding": True,
+    "torch_dtype": "bfloat16", "bos_token_id": 1, "eos_token_id": 7,
+}
+CONTEXT = 4096
+PREFILL_TOKENS = 2048
+PAGE = 16
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        with open(path) as f:
+            m = json.load(f)
+        return {"hbm_gbs": float(m["hbm_gbs"]), "bf16_tflops": float(m["bf16_tflops"]),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi samples during the timed region: SM clock and throttle reasons."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        clocks, reasons, mx = [], set(), None
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        with open(self.path) as f:
+            for line in f:
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) < 6:
+                    continue
+                try:
+                    clocks.append(float(parts[0]))
+                    mx = float(parts[1])
+                except ValueError:
+                    continue
+                for name, val in zip(names, parts[2:6]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+        os.remove(self.path)
+        if clocks:
+            clocks.sort()
+            out["sm_mhz"] = clocks[len(clocks) // 2]
+            out["sm_max_mhz"] = mx
+        out["reasons"] = sorted(reasons)
+        return out
+
+
+def model_bytes_and_flops(cfg, spec_decls):
+    """Bytes of every weight a step reads once, and matrix FLOPs per token."""
+    weight_bytes = 0
+    matmul_params = 0
+    for name, decl in spec_decls.items():
+        n = 1
+        for d in decl.shape:
+            n *= d
+        weight_bytes += n * 2
+        if len(decl.shape) == 2 and "embed_tokens" not in name and "conv.conv" not in name:
+            matmul_params += n
+    return weight_bytes, matmul_params
+
+
+def run_ours(args):
+    import torch
+
+    from rvllm_b200.config import architecture, config_from_dict
+    from rvllm_b200.engine import (Engine, ModelRunner, Request, SchedulerConfig, StepEntry,
+                                   load_model, make_cache)
+    from rvllm_b200.parts.model import param_decls
+    from rvllm_b200.sampling import SamplingParams
+    from rvllm_b200.weights import write_random_model
+
+    pk = peaks()
+    layers_full = LFM2_1_2B["num_hidden_layers"]
+    data = dict(LFM2_1_2B)
+    cfg = config_from_dict(data)
+    K, W, B = args.steps, args.warmup, args.batch
+    if K + W > CONTEXT - 64:
+        raise SystemExit(f"--steps + --warmup must stay below {CONTEXT - 64}")
+    tmp = tempfile.mkdtemp(prefix="rvllm_bench_")
+    t0 = time.time()
+    folder = write_random_model(os.path.join(tmp, "lfm2_1_2b"), cfg, seed=0)
+    model, cfg = load_model(folder, "bfloat16", "cuda")
+    for f in os.listdir(folder):
+        os.remove(os.path.join(folder, f))
+    os.rmdir(folder)
+    os.rmdir(tmp)
+    setup_s = time.time() - t0
+    ops = model.ops
+    spec = architecture(cfg.architecture).build_spec(cfg)
+    weight_bytes, matmul_params = model_bytes_and_flops(cfg, param_decls(spec))
+    n_attn = len(cfg.full_attn_idxs)
+    n_conv = cfg.num_hidden_layers - n_attn
+    kv_bytes_per_token = n_attn * 2 * cfg.num_key_value_heads * cfg.head_dim * 2
+    conv_state_bytes = n_conv * (cfg.conv_L_cache - 1) * cfg.hidden_size * 4 * 2   # read + write
+    gen = torch.Generator().manual_seed(0)
+
+    def prompts(n, length):
+        return torch.randint(0, cfg.vocab_size, (n, length), generator=gen).tolist()
+
+    def fresh_runner(batch):
+        pages = batch * (CONTEXT // PAGE)
+        cache = make_cache(model, PAGE, pages, batch)
+        return ModelRunner(model, cache, ops, use_graphs=True)
+
+    def do_prefill(runner, ids_list, chunk=2048):
+        for i, ids in enumerate(ids_list):
+            runner.add_request(i)
+            for a in range(0, len(ids), chunk):
+                runner.step([StepEntry(i, ids[a:a + chunk], ())])
+
+    def timed_decode(batch, start_ctx, steps, warmup):
+        """Device-timed greedy decode: tokens fed back on the device."""
+        runner = fresh_runner(batch)
+        do_prefill(runner, prompts(batch, start_ctx - warmup))
+        reqs = list(range(batch))
+        first = [1] * batch
+        out = runner.decode_greedy(reqs, first, warmup)
+        first = out[-1].tolist() if warmup else first
+        torch.cuda.synchronize()
+        launches0 = ops.launches
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        runner.decode_greedy(reqs, first, steps)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        return batch * steps / (ms / 1e3), ms / steps, ops.launches - launches0
+
+    # ---- the headline: batch B, K steps ending at the full context ------------------
+    sampler = ClockSampler()
+    sampler.start()
+    value, ms_per_step, launches = timed_decode(B, CONTEXT - K, K, W)
+    clocks = sampler.stop()
+    mean_ctx = CONTEXT - K / 2
+    step_bytes = weight_bytes + B * mean_ctx * kv_bytes_per_token + B * conv_state_bytes
+    achieved = step_bytes / (ms_per_step / 1e3) / 1e9
+
+    # ---- end to end through Engine.step ------------------------------------------------
+    runner = fresh_runner(B)
+    sched = SchedulerConfig(block_size=PAGE, num_blocks=B * (CONTEXT // PAGE),
+                            max_num_batched_tokens=8192, prefill_chunk=2048)
+    engine = Engine(runner, sched, CONTEXT)
+    e2e_steps = min(K, 512)
+    budget = e2e_steps + W + 16          # requests start decoding a few steps apart
+    for i, ids in enumerate(prompts(B, CONTEXT - budget)):
+        engine.add_request(Request(i, ids, budget, (), SamplingParams()))
+    seqs = list(engine.scheduler.seqs.values())
+    while min(len(s.generated) for s in seqs) < W:
+        engine.step()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    done = 0
+    for _ in range(e2e_steps):
+        done += len(engine.step())
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    e2e = {"value": round(done / e2e_s, 1), "unit": "tokens/s",
+           "h2d_bytes_per_step": runner.builder.last_h2d_bytes, "d2h_bytes_per_step": 4 * B}
+    del engine, runner
+
+    # ---- prefill of 2,048 tokens -----------------------------------------------------
+    runner = fresh_runner(1)
+    ids = prompts(1, PREFILL_TOKENS)[0]
+    times = []
+    for it in range(5):
+        runner.add_request("p")
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        runner.step([StepEntry("p", ids, (PREFILL_TOKENS - 1,))])
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+        runner.end_request("p")
+    pre_ms = sorted(times[2:])[len(times[2:]) // 2]
+    T = PREFILL_TOKENS
+    flops = 2.0 * T * matmul_params + 2.0 * cfg.vocab_size * cfg.hidden_size \
+        + n_attn * 4.0 * cfg.num_attention_heads * cfg.head_dim * T * (T + 1) / 2
+    prefill = {"value": round(T / (pre_ms / 1e3), 1), "tokens": T, "ms": round(pre_ms, 3),
+               "frac": round(flops / (pre_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
+    del runner
+
+    # ---- other batch sizes -------------------------------------------------------------
+    points = {}
+    for b in (1, 64):
+        v, _, _ = timed_decode(b, 2048, 256, 3)
+        points[f"decode_b{b}"] = round(v, 1)
+
+    line = {
+        "metric": "decode tok/s at batch 8 (LFM2-1.2B sizes, context to 4,096)",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
+        "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic: random weights (seed 0), "
+        "uniform random token ids", "impl": "ours",
+        "config": {"model": "LFM2-1.2B sizes", "layers": cfg.num_hidden_layers,
+                   "layers_full": layers_full, "hidden": cfg.hidden_size,
+                   "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
+                   "head_dim": cfg.head_dim, "ffn": cfg.ffn_dim, "vocab": cfg.vocab_size,
+                   "conv_taps": cfg.conv_L_cache, "attn_layers": n_attn,
+                   "global_batch": B, "seq_len": CONTEXT, "page": PAGE,
+                   "parallelism": "single GPU", "l2": "inputs larger than L2 (2.3 GB weights)",
+                   "peaks": pk["source"]},
+        "e2e": e2e, "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"],
+                     "unit": "GB/s", "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": points, "gpu_launches": launches, "clocks": clocks,
+        "setup_s": round(setup_s, 1),
+    }
+    print(json.dumps(line))
+    return 0
+
+
+def run_reference(args):
+    print(json.dumps({
+        "impl": "reference",
+        "unavailable": "ermolushka/rvllm is a Rust crate (no setup.py/pyproject.toml: pip says "
+                       "'not installable'); no cargo/rustc and no vendored crates offline"}))
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=1024)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+    return run_ours(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

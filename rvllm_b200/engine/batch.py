@@ -78,6 +78,7 @@ class BatchBuilder:
         self._host = None
         self._dev = None
         self._copied = None         # event: the last copy out of the host buffer is done
+        self.last_h2d_bytes = 0
 
     def _buffers(self, words: int):
         if self._host is None or self._host.numel() < words:
@@ -121,7 +122,9 @@ class BatchBuilder:
         for gi in range(n_groups):
             mb = max([-(-c // ps) for c in ctx] + [1])
             max_blocks.append(max(mb, pad_blocks))
-        M = sum(len(e.want) for e in entries)
+        # a padded (replayed) step produces the logits of every row, padding included, so
+        # that the captured launch sizes do not depend on how many requests are real
+        M = N if pad_reqs else sum(len(e.want) for e in entries)
 
         # layout, in int32 words
         off = {}
@@ -169,7 +172,9 @@ class BatchBuilder:
         ss = view("state_slot"); ss[:r_real] = [rc.slot for rc in rcs]; ss[r_real:] = -1
         rows = view("logit_rows")
         k = 0
-        for i, e in enumerate(entries):
+        if pad_reqs:
+            rows[:] = np.arange(N)
+        for i, e in enumerate(entries if not pad_reqs else ()):
             for w in e.want:
                 if not 0 <= w < q_lens[i]:
                     raise ValueError(f"request {e.req!r}: wanted place {w} is outside "
@@ -193,6 +198,7 @@ class BatchBuilder:
                 a = int(q_start[i])
                 slots[a:a + q] = pages * ps + p % ps
         dev[:cur].copy_(host[:cur], non_blocking=True)
+        self.last_h2d_bytes = cur * 4
         if dev.is_cuda:
             if self._copied is None:
                 self._copied = torch.cuda.Event()

@@ -93,15 +93,44 @@ class ModelRunner:
         self.steps += 1
         return logits
 
-    def _run(self, ordered: List[StepEntry]) -> torch.Tensor:
+    def _run(self, ordered: List[StepEntry], device_tokens=None) -> torch.Tensor:
         if self.use_graphs and all(len(e.tokens) == 1 for e in ordered):
-            return self._run_graph(ordered)
+            return self._run_graph(ordered, device_tokens)
         ctx = self.builder.build(ordered)
+        if device_tokens is not None:
+            ctx.token_ids[:len(ordered)].copy_(device_tokens)
         return self.model.forward(ctx, self.cache.views())
+
+    def decode_greedy(self, reqs: Sequence[Hashable], first_tokens: Sequence[int],
+                      steps: int) -> torch.Tensor:
+        """`steps` greedy single-token steps for live requests `reqs` with no host round
+        trip: the argmax of one step is the next step's token, on the device.  Returns
+        the sampled ids, int32 [steps, len(reqs)], on the device.  The first row are the
+        successors of `first_tokens`."""
+        r = len(reqs)
+        prev = torch.tensor(list(first_tokens), dtype=torch.int32, device=self.device)
+        out = torch.empty((steps, r), dtype=torch.int32, device=self.device)
+        for k in range(steps):
+            entries = [StepEntry(q, (0,), (0,)) for q in reqs]
+            for e in entries:
+                total = self.cache.requests[e.req].computed + 1
+                if total > self.model.spec.max_position:
+                    raise ValueError(f"request {e.req!r}: {total} tokens exceed the model's "
+                                     f"{self.model.spec.max_position} positions")
+                if not self.cache.reserve(e.req, total):
+                    raise CacheError(f"out of pages: request {e.req!r} needs room for "
+                                     f"{total} tokens")
+            logits = self._run(entries, device_tokens=prev)
+            prev = self.ops.argmax(logits[:r])
+            out[k].copy_(prev)
+            for e in entries:
+                self.cache.advance(e.req, self.cache.requests[e.req].computed + 1)
+            self.steps += 1
+        return out
 
     # ---- replayed single-token steps ---------------------------------------------------
 
-    def _run_graph(self, ordered: List[StepEntry]) -> torch.Tensor:
+    def _run_graph(self, ordered: List[StepEntry], device_tokens=None) -> torch.Tensor:
         ps = self.cache.page_size
         r = len(ordered)
         bucket = 1 << (r - 1).bit_length()
@@ -109,13 +138,13 @@ class ModelRunner:
         blocks = -(-ctx_max // ps)
         block_bucket = max(16, 1 << (blocks - 1).bit_length())
         # every row's logits are produced inside the graph; the wanted ones are picked after
-        full = [StepEntry(e.req, e.tokens, (0,)) for e in ordered]
+        full = ordered
         key = (bucket, block_bucket)
         g = self._graphs.get(key)
         if g is None:
             g = _DecodeGraph(self, bucket, block_bucket)
             self._graphs[key] = g
-        logits = g.run(full)
+        logits = g.run(full, device_tokens)
         self.graph_steps += 1
         rows = [i for i, e in enumerate(ordered) for _ in e.want]
         if rows == list(range(r)):
@@ -147,7 +176,7 @@ class _DecodeGraph:
         ctx.max_ctx_len = self.block_bucket * self.runner.cache.page_size
         return ctx
 
-    def run(self, entries) -> torch.Tensor:
+    def run(self, entries, device_tokens=None) -> torch.Tensor:
         model, views = self.runner.model, self.runner.cache.views()
         if self.graph is None:
             # An eager run over padding only comes first: it initialises the matrix
@@ -158,11 +187,18 @@ class _DecodeGraph:
             model.forward(warm, views)
             torch.cuda.synchronize()
             ctx = self._build(entries)
+            if device_tokens is not None:
+                ctx.token_ids[:len(entries)].copy_(device_tokens)
             torch.cuda.synchronize()
+            launches = model.ops.launches
             self.graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(self.graph):
                 self.logits = model.forward(ctx, views)
+            self.kernels_per_replay = model.ops.launches - launches
         else:
-            self._build(entries)
+            ctx = self._build(entries)
+            if device_tokens is not None:
+                ctx.token_ids[:len(entries)].copy_(device_tokens)
         self.graph.replay()
+        model.ops.launches += self.kernels_per_replay
         return self.logits

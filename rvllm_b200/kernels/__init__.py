@@ -9,6 +9,6 @@ def cuda_ops():
     device or the native library cannot be built or loaded."""
     global _OPS
     if _OPS is None:
-        from .cuda_ops import CudaOps
+        from .bindings import CudaOps
         _OPS = CudaOps()
     return _OPS
