@@ -131,7 +131,7 @@ def run_ours(args):
 
     from rvllm_b200.config import architecture, config_from_dict
     from rvllm_b200.engine import (Engine, ModelRunner, Request, SchedulerConfig, StepEntry,
-                                   load_model, make_cache)
+                                   graphs_default, load_model, make_cache)
     from rvllm_b200.parts.model import param_decls
     from rvllm_b200.sampling import SamplingParams
     from rvllm_b200.weights import write_random_model
@@ -167,7 +167,7 @@ def run_ours(args):
     def fresh_runner(batch):
         pages = batch * (CONTEXT // PAGE)
         cache = make_cache(model, PAGE, pages, batch)
-        return ModelRunner(model, cache, ops, use_graphs=True)
+        return ModelRunner(model, cache, ops, use_graphs=graphs_default())
 
     def do_prefill(runner, ids_list, chunk=2048):
         for i, ids in enumerate(ids_list):
@@ -193,6 +193,9 @@ def run_ours(args):
         ms = e0.elapsed_time(e1)
         return batch * steps / (ms / 1e3), ms / steps, ops.launches - launches0
 
+    if args.only == "prefill":
+        return run_prefill_only(torch, fresh_runner, prompts, StepEntry)
+
     # ---- the headline: batch B, K steps ending at the full context ------------------
     sampler = ClockSampler()
     sampler.start()
@@ -201,6 +204,12 @@ def run_ours(args):
     mean_ctx = CONTEXT - K / 2
     step_bytes = weight_bytes + B * mean_ctx * kv_bytes_per_token + B * conv_state_bytes
     achieved = step_bytes / (ms_per_step / 1e3) / 1e9
+
+    if args.only == "decode":
+        print(json.dumps({"only": "decode", "value": round(value, 1),
+                          "ms_per_step": round(ms_per_step, 4), "gpu_launches": launches,
+                          "roofline_gbs": round(achieved, 1), "clocks": clocks}))
+        return 0
 
     # ---- end to end through Engine.step ------------------------------------------------
     runner = fresh_runner(B)
@@ -277,6 +286,24 @@ def run_ours(args):
     return 0
 
 
+def run_prefill_only(torch, fresh_runner, prompts, StepEntry):
+    runner = fresh_runner(1)
+    ids = prompts(1, PREFILL_TOKENS)[0]
+    times = []
+    for it in range(3):
+        runner.add_request("p")
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        runner.step([StepEntry("p", ids, (PREFILL_TOKENS - 1,))])
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+        runner.end_request("p")
+    print(json.dumps({"only": "prefill", "ms": [round(t, 3) for t in times]}))
+    return 0
+
+
 def run_reference(args):
     print(json.dumps({
         "impl": "reference",
@@ -292,6 +319,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
+                    help="run one part only (for profiling); the JSON line then lacks the rest")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)

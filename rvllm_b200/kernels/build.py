@@ -120,6 +120,13 @@ def build(verbose: bool = True, force: bool = False) -> str:
             if r.returncode != 0:
                 raise KernelError(f"linking the kernel library failed:\n{r.stderr[-4000:]}")
             os.replace(tmp_out, out)
+            for old in os.listdir(os.path.dirname(out)):       # libraries of older sources
+                if old.startswith("librvllm_b200_") and old.endswith(".so") and \
+                        os.path.join(os.path.dirname(out), old) != out:
+                    try:
+                        os.remove(os.path.join(os.path.dirname(out), old))
+                    except OSError:
+                        pass
         finally:
             shutil.rmtree(work, ignore_errors=True)
         _say(f"built {os.path.basename(out)} in {time.time() - t0:.0f} s", verbose)
