@@ -1,0 +1,390 @@
+// Paged grouped-query attention on the tensor cores for bfloat16 storage: flash-style
+// prefill, and split-KV decode, from one kernel template.  Compiled once per head size
+// (-DRV_HD=<multiple of 16, at most 128>), at the first use of a model with that size.
+//
+// Work layout.  The query rows of one (request, key/value head) are *packed*: row m is
+// (token m / G, query head g*G + m % G), G = heads per key/value head, so the G query
+// heads that share a key/value head sit side by side in the M dimension of the matrix
+// instruction and every key and value tile is read once for all of them.  A block owns
+// 16 * NWARPS packed rows and walks the key tiles of 64 keys that those rows can see;
+// tiles are aligned to absolute position 0, so the order of every sum depends on
+// positions only, not on how the tokens were cut into steps.
+//   prefill  NWARPS = 4, the block walks all its tiles and writes the output rows.
+//   decode   NWARPS = 1, one token per request; the block walks the tiles of one split of
+//            256 keys and writes unnormalised partial results, which
+//            paged_attention_merge_kernel (attention_simt.cu) combines in split order.
+// Per tile: S = Q K^T (mma.sync m16n8k16, float32 accumulators), mask by comparison,
+// online softmax in float32 (base-2 exponentials of scores pre-multiplied by
+// scale * log2 e), P rounded to bfloat16, O += P V.  K and V tiles come from the pages
+// through the block table with 16-byte cp.async copies into padded shared-memory rows,
+// two stages deep; keys past the context or in released pages are zero-filled.
+//
+// Reference counterparts: kv_gather.cu (twice), a batched SGEMM, mask_add_broadcast.cu,
+// softmax.cu, a batched SGEMM and transposes (src/cuda/model.rs:528-581).  Plain
+// reference: tests/plain_ops.py paged_attention.
+#include "common.cuh"
+
+#ifndef RV_HD
+#error "compile with -DRV_HD=<head size>"
+#endif
+#if RV_HD % 16 != 0 || RV_HD > 128 || RV_HD < 16
+#error "RV_HD must be a multiple of 16 between 16 and 128"
+#endif
+
+#define RV_BN 64                 // keys per tile
+#define RV_SPLIT 256             // keys per decode split (must match attention_simt.cu)
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ void cp_async_16(void* smem, const void* gmem, bool valid) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    const int bytes = valid ? 16 : 0;   // 0 source bytes: the 16 destination bytes are zeroed
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* smem) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const void* smem) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0,
+                                         unsigned b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+        "{%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *(unsigned*)&v;
+}
+
+template <int HD, int NWARPS, bool SPLIT>
+__global__ void __launch_bounds__(NWARPS * 32) paged_attention_mma_kernel(
+    const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ k_cache,
+    const bf16* __restrict__ v_cache, const int* __restrict__ block_table, int max_blocks,
+    const int* __restrict__ q_start, const int* __restrict__ ctx_lens, bf16* __restrict__ out,
+    float* __restrict__ part_o, float2* __restrict__ part_ml, int max_splits, int first_req,
+    int num_heads, int num_kv_heads, int page_size, float scale_log2, int window) {
+    constexpr int BM = 16 * NWARPS;
+    constexpr int LD = HD + 8;          // padded row: conflict-free ldmatrix for HD % 16 == 0
+    constexpr int CPR = HD / 8;         // 16-byte chunks per row
+    constexpr int KSTEPS = HD / 16;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* Qs = (bf16*)smem_raw;                         // [BM][LD]
+    bf16* Ks = Qs + BM * LD;                            // [2][BN][LD]
+    bf16* Vs = Ks + 2 * RV_BN * LD;                     // [2][BN][LD]
+
+    const int G = num_heads / num_kv_heads;
+    const int r = first_req + blockIdx.z;
+    const int clen = ctx_lens[r];
+    if (clen == 0) return;
+    const int qs = q_start[r];
+    const int qlen = SPLIT ? 1 : q_start[r + 1] - qs;
+    const int rows_total = qlen * G;
+    int g, tile, split = 0;
+    if (SPLIT) {
+        const int tiles_per_head = (G + BM - 1) / BM;
+        g = blockIdx.y / tiles_per_head;
+        tile = blockIdx.y % tiles_per_head;
+        split = blockIdx.x;
+    } else {
+        g = blockIdx.y;
+        tile = gridDim.x - 1 - blockIdx.x;              // heaviest (latest) rows first
+    }
+    const int m0 = tile * BM;
+    if (m0 >= rows_total) return;
+    const int pos0 = clen - qlen;                        // position of the request's first token here
+    const int tok_lo = m0 / G;
+    const int tok_hi = min(rows_total - 1, m0 + BM - 1) / G;
+    int key_lo = window > 0 ? max(0, pos0 + tok_lo - window + 1) : 0;
+    int key_hi = pos0 + tok_hi;                          // inclusive
+    if (SPLIT) {
+        key_lo = max(key_lo, split * RV_SPLIT);
+        key_hi = min(key_hi, split * RV_SPLIT + RV_SPLIT - 1);
+        if (key_lo > key_hi) return;
+    }
+    const int tile_begin = key_lo / RV_BN, tile_end = key_hi / RV_BN;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int* table = block_table + (size_t)r * max_blocks;
+    const size_t kv_row = (size_t)num_kv_heads * HD;
+
+    // ---- Q tile -> shared memory (packed rows), zero beyond the last row ----------------
+    for (int c = tid; c < BM * CPR; c += NWARPS * 32) {
+        const int m = c / CPR, ch = c - m * CPR;
+        const int row = m0 + m;
+        const bool valid = row < rows_total;
+        const int tok = valid ? row / G : 0, hg = valid ? row - tok * G : 0;
+        const bf16* src = q + (size_t)(qs + tok) * q_stride + (size_t)(g * G + hg) * HD + ch * 8;
+        cp_async_16(Qs + m * LD + ch * 8, src, valid);
+    }
+    auto load_tile = [&](int t, int stage) {
+        bf16* kd = Ks + stage * RV_BN * LD;
+        bf16* vd = Vs + stage * RV_BN * LD;
+        for (int c = tid; c < RV_BN * CPR; c += NWARPS * 32) {
+            const int row = c / CPR, ch = c - row * CPR;
+            const int j = t * RV_BN + row;
+            int page = -1;
+            if (j < clen) page = table[j / page_size];
+            const bool valid = page >= 0;
+            const size_t off = valid ? ((size_t)page * page_size + j % page_size) * kv_row +
+                                           (size_t)g * HD + ch * 8 : 0;
+            cp_async_16(kd + row * LD + ch * 8, k_cache + off, valid);
+            cp_async_16(vd + row * LD + ch * 8, v_cache + off, valid);
+        }
+    };
+    load_tile(tile_begin, 0);
+    cp_async_commit();
+
+    // ---- per-thread state: rows lane/4 and lane/4 + 8 of this warp's 16 rows ------------
+    const int row_a = m0 + warp * 16 + (lane >> 2), row_b = row_a + 8;
+    const bool ok_a = row_a < rows_total, ok_b = row_b < rows_total;
+    const int p_a = ok_a ? pos0 + row_a / G : -1, p_b = ok_b ? pos0 + row_b / G : -1;
+    int lo_a = window > 0 ? max(0, p_a - window + 1) : 0;
+    int lo_b = window > 0 ? max(0, p_b - window + 1) : 0;
+    int hi_a = p_a, hi_b = p_b;
+    if (SPLIT) {
+        lo_a = max(lo_a, key_lo); lo_b = max(lo_b, key_lo);
+        hi_a = min(hi_a, key_hi); hi_b = min(hi_b, key_hi);
+    }
+    float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
+    float o[HD / 8][4];
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    unsigned qf[KSTEPS][4];
+    bool q_loaded = false;
+
+    for (int t = tile_begin; t <= tile_end; ++t) {
+        const int stage = (t - tile_begin) & 1;
+        if (t + 1 <= tile_end) {
+            load_tile(t + 1, stage ^ 1);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        if (!q_loaded) {
+            q_loaded = true;
+#pragma unroll
+            for (int kk = 0; kk < KSTEPS; ++kk)
+                ldmatrix_x4(qf[kk], Qs + (warp * 16 + (lane & 15)) * LD + kk * 16 + (lane >> 4) * 8);
+        }
+        const bf16* kt = Ks + stage * RV_BN * LD;
+        const bf16* vt = Vs + stage * RV_BN * LD;
+
+        // S = Q K^T for 16 rows x 64 keys
+        float s[RV_BN / 8][4];
+#pragma unroll
+        for (int i = 0; i < RV_BN / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+#pragma unroll
+        for (int kk = 0; kk < KSTEPS; ++kk) {
+#pragma unroll
+            for (int nb = 0; nb < RV_BN / 16; ++nb) {
+                unsigned b[4];
+                ldmatrix_x4(b, kt + (nb * 16 + (lane & 7) + (lane >> 4) * 8) * LD + kk * 16 +
+                                   ((lane >> 3) & 1) * 8);
+                mma_bf16(s[2 * nb], qf[kk], b[0], b[1]);
+                mma_bf16(s[2 * nb + 1], qf[kk], b[2], b[3]);
+            }
+        }
+        // mask, scale, running maximum
+        const int key0 = t * RV_BN + (lane & 3) * 2;
+        float mx_a = -INFINITY, mx_b = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < RV_BN / 8; ++i) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int key = key0 + i * 8 + e;
+                s[i][e] = (key >= lo_a && key <= hi_a) ? s[i][e] * scale_log2 : -INFINITY;
+                s[i][2 + e] = (key >= lo_b && key <= hi_b) ? s[i][2 + e] * scale_log2 : -INFINITY;
+                mx_a = fmaxf(mx_a, s[i][e]);
+                mx_b = fmaxf(mx_b, s[i][2 + e]);
+            }
+        }
+        mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
+        mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
+        mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
+        mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+        const float mn_a = fmaxf(m_a, mx_a), mn_b = fmaxf(m_b, mx_b);
+        const float off_a = mn_a == -INFINITY ? 0.f : mn_a, off_b = mn_b == -INFINITY ? 0.f : mn_b;
+        const float corr_a = exp2f(m_a - off_a), corr_b = exp2f(m_b - off_b);   // m = -inf -> 0
+        m_a = mn_a;
+        m_b = mn_b;
+        l_a *= corr_a;
+        l_b *= corr_b;
+#pragma unroll
+        for (int i = 0; i < HD / 8; ++i) {
+            o[i][0] *= corr_a; o[i][1] *= corr_a;
+            o[i][2] *= corr_b; o[i][3] *= corr_b;
+        }
+        // P = exp2(S - m), rounded to bfloat16 for the second product; the row sum adds the
+        // rounded values, so numerator and denominator see the same numbers
+        unsigned pa[RV_BN / 16][4];
+#pragma unroll
+        for (int i = 0; i < RV_BN / 8; ++i) {
+            const float e0 = exp2f(s[i][0] - off_a), e1 = exp2f(s[i][1] - off_a);
+            const float e2 = exp2f(s[i][2] - off_b), e3 = exp2f(s[i][3] - off_b);
+            const __nv_bfloat162 ra = __floats2bfloat162_rn(e0, e1);
+            const __nv_bfloat162 rb = __floats2bfloat162_rn(e2, e3);
+            const float2 fa = __bfloat1622float2(ra), fb = __bfloat1622float2(rb);
+            l_a += fa.x + fa.y;
+            l_b += fb.x + fb.y;
+            pa[i >> 1][(i & 1) * 2] = *(const unsigned*)&ra;
+            pa[i >> 1][(i & 1) * 2 + 1] = *(const unsigned*)&rb;
+        }
+        // O += P V
+#pragma unroll
+        for (int kk = 0; kk < RV_BN / 16; ++kk) {
+#pragma unroll
+            for (int nd = 0; nd < HD / 16; ++nd) {
+                unsigned b[4];
+                ldmatrix_x4_trans(b, vt + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LD +
+                                         nd * 16 + (lane >> 4) * 8);
+                mma_bf16(o[2 * nd], pa[kk], b[0], b[1]);
+                mma_bf16(o[2 * nd + 1], pa[kk], b[2], b[3]);
+            }
+        }
+        __syncthreads();    // every warp is done with this stage before it is refilled
+    }
+    l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
+    l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+    l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
+    l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+
+    const int col = (lane & 3) * 2;
+    if (SPLIT) {
+        const float ln2 = 0.6931471805599453f;
+        if (ok_a) {
+            const size_t slot = ((size_t)r * num_heads + g * G + row_a) * max_splits + split;
+#pragma unroll
+            for (int i = 0; i < HD / 8; ++i)
+                *(float2*)(part_o + slot * HD + i * 8 + col) = make_float2(o[i][0], o[i][1]);
+            if ((lane & 3) == 0) part_ml[slot] = make_float2(m_a * ln2, l_a);
+        }
+        if (ok_b) {
+            const size_t slot = ((size_t)r * num_heads + g * G + row_b) * max_splits + split;
+#pragma unroll
+            for (int i = 0; i < HD / 8; ++i)
+                *(float2*)(part_o + slot * HD + i * 8 + col) = make_float2(o[i][2], o[i][3]);
+            if ((lane & 3) == 0) part_ml[slot] = make_float2(m_b * ln2, l_b);
+        }
+    } else {
+        if (ok_a) {
+            const int tok = row_a / G, hg = row_a - tok * G;
+            bf16* dst = out + (size_t)(qs + tok) * num_heads * HD + (size_t)(g * G + hg) * HD + col;
+            const float inv = 1.f / l_a;
+#pragma unroll
+            for (int i = 0; i < HD / 8; ++i)
+                *(unsigned*)(dst + i * 8) = pack_bf16(o[i][0] * inv, o[i][1] * inv);
+        }
+        if (ok_b) {
+            const int tok = row_b / G, hg = row_b - tok * G;
+            bf16* dst = out + (size_t)(qs + tok) * num_heads * HD + (size_t)(g * G + hg) * HD + col;
+            const float inv = 1.f / l_b;
+#pragma unroll
+            for (int i = 0; i < HD / 8; ++i)
+                *(unsigned*)(dst + i * 8) = pack_bf16(o[i][2] * inv, o[i][3] * inv);
+        }
+    }
+}
+
+static thread_local char g_error[512] = "";
+static int fail(const char* msg) {
+    snprintf(g_error, sizeof(g_error), "%s", msg);
+    return 1;
+}
+#define RV_CAT2(a, b) a##b
+#define RV_CAT(a, b) RV_CAT2(a, b)
+#define RV_SYM(name) RV_CAT(RV_CAT(name, _hd), RV_HD)
+
+extern "C" const char* RV_SYM(rv_attention_mma_last_error)() { return g_error; }
+
+template <int NWARPS>
+static size_t smem_bytes() {
+    return (size_t)(16 * NWARPS + 4 * RV_BN) * (RV_HD + 8) * sizeof(bf16);
+}
+
+// Prefill: requests [first_req, first_req + n_reqs), the longest bringing max_q_len tokens.
+extern "C" int RV_SYM(rv_paged_attention_prefill_mma)(
+    const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* block_table,
+    int max_blocks, const int* q_start, const int* ctx_lens, void* out, int first_req, int n_reqs,
+    int max_q_len, int num_heads, int num_kv_heads, int page_size, float scale, int window,
+    void* stream) {
+    if (n_reqs == 0) return 0;
+    if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads || page_size <= 0 ||
+        max_q_len <= 0 || n_reqs < 0)
+        return fail("paged_attention_prefill_mma: bad sizes");
+    const int G = num_heads / num_kv_heads;
+    const long long tiles = ((long long)max_q_len * G + 63) / 64;
+    if (tiles > 0x7fffffffLL || num_kv_heads > 65535 || n_reqs > 65535)
+        return fail("paged_attention_prefill_mma: batch too large for one launch");
+    static bool configured = false;
+    const size_t smem = smem_bytes<4>();
+    if (!configured && smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(paged_attention_mma_kernel<RV_HD, 4, false>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return fail(cudaGetErrorString(e));
+        configured = true;
+    }
+    dim3 grid((unsigned)tiles, num_kv_heads, n_reqs);
+    paged_attention_mma_kernel<RV_HD, 4, false><<<grid, 128, smem, (cudaStream_t)stream>>>(
+        (const bf16*)q, q_stride, (const bf16*)k_cache, (const bf16*)v_cache, block_table,
+        max_blocks, q_start, ctx_lens, (bf16*)out, nullptr, nullptr, 0, first_req, num_heads,
+        num_kv_heads, page_size, scale * 1.4426950408889634f, window);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(cudaGetErrorString(e));
+    return 0;
+}
+
+// Decode: requests [0, n_reqs) bring one token each (token index == request index).
+// Writes partial results for paged_attention_merge_kernel; scratch layout as in
+// rv_paged_attention_decode: part_o [n_reqs * heads * max_splits][HD], then part_ml.
+extern "C" int RV_SYM(rv_paged_attention_decode_mma)(
+    const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* block_table,
+    int max_blocks, const int* q_start, const int* ctx_lens, void* scratch, long long scratch_bytes,
+    int n_reqs, int max_ctx_len, int num_heads, int num_kv_heads, int page_size, float scale,
+    int window, void* stream) {
+    if (n_reqs == 0) return 0;
+    if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads || page_size <= 0 ||
+        n_reqs < 0)
+        return fail("paged_attention_decode_mma: bad sizes");
+    int max_splits = (max_ctx_len + RV_SPLIT - 1) / RV_SPLIT;
+    if (max_splits < 1) max_splits = 1;
+    const size_t slots = (size_t)n_reqs * num_heads * max_splits;
+    if ((long long)(slots * RV_HD * 4 + slots * 8) > scratch_bytes)
+        return fail("paged_attention_decode_mma: scratch too small");
+    const int G = num_heads / num_kv_heads;
+    const int tiles_per_head = (G + 15) / 16;
+    if (n_reqs > 65535 || num_kv_heads * tiles_per_head > 65535)
+        return fail("paged_attention_decode_mma: batch too large for one launch");
+    static bool configured = false;
+    const size_t smem = smem_bytes<1>();
+    if (!configured && smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(paged_attention_mma_kernel<RV_HD, 1, true>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return fail(cudaGetErrorString(e));
+        configured = true;
+    }
+    dim3 grid(max_splits, num_kv_heads * tiles_per_head, n_reqs);
+    float* part_o = (float*)scratch;
+    float2* part_ml = (float2*)((char*)scratch + slots * RV_HD * 4);
+    paged_attention_mma_kernel<RV_HD, 1, true><<<grid, 32, smem, (cudaStream_t)stream>>>(
+        (const bf16*)q, q_stride, (const bf16*)k_cache, (const bf16*)v_cache, block_table,
+        max_blocks, q_start, ctx_lens, nullptr, part_o, part_ml, max_splits, 0, num_heads,
+        num_kv_heads, page_size, scale * 1.4426950408889634f, window);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(cudaGetErrorString(e));
+    return 0;
+}

@@ -387,3 +387,25 @@ extern "C" int rv_paged_attention_decode(const void* q, int dtype, int q_stride,
     RV_CHECK_LAUNCH("paged_attention_merge");
     return 0;
 }
+
+// The merge step alone, for partial results written by another kernel (attention_mma.cu)
+// in the same scratch layout.
+extern "C" int rv_paged_attention_merge(const void* scratch, const int* ctx_lens, void* out,
+                                        int dtype, int n_reqs, int max_ctx_len, int num_heads,
+                                        int hd, int window, void* stream) {
+    if (n_reqs == 0) return 0;
+    int max_splits = (max_ctx_len + RV_ATTN_SPLIT - 1) / RV_ATTN_SPLIT;
+    if (max_splits < 1) max_splits = 1;
+    if (n_reqs < 0 || n_reqs > 65535 || num_heads <= 0 || hd <= 0)
+        RV_FAIL("paged_attention_merge: bad sizes");
+    const size_t slots = (size_t)n_reqs * num_heads * max_splits;
+    const float* part_o = (const float*)scratch;
+    const float2* part_ml = (const float2*)((const char*)scratch + slots * hd * 4);
+    dim3 mgrid(num_heads, n_reqs);
+    const int threads = hd < 32 ? 32 : (hd > 128 ? 128 : ((hd + 31) / 32) * 32);
+    RV_DISPATCH_DTYPE(dtype, "paged_attention_merge",
+        (paged_attention_merge_kernel<T><<<mgrid, threads, 0, (cudaStream_t)stream>>>(
+            part_o, part_ml, ctx_lens, (T*)out, max_splits, num_heads, hd, window)));
+    RV_CHECK_LAUNCH("paged_attention_merge");
+    return 0;
+}

@@ -11,12 +11,13 @@ path here: constructing `CudaOps` without a CUDA device or without the library r
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_longlong, c_void_p
 
 import torch
 
 from ..errors import KernelError
-from .build import build
+from .build import build, build_variant
 
 _F32, _BF16 = 0, 1
 
@@ -48,6 +49,12 @@ class CudaOps:
         self.lib.rv_last_error.restype = ctypes.c_char_p
         self.lib.rv_paged_attention_decode_scratch_bytes.restype = c_longlong
         self._scratch = {}
+        self._attn_libs = {}
+        self._verbose_build = verbose_build
+        # bfloat16 attention: "mma" = tensor-core kernels (attention_mma.cu, head sizes that
+        # are multiples of 16 up to 128), "simt" = the float32-arithmetic kernels
+        self.prefill_attention = os.environ.get("RVLLM_PREFILL_ATTENTION", "mma")
+        self.decode_attention = os.environ.get("RVLLM_DECODE_ATTENTION", "mma")
         # float32 products must be float32: no TF32, no reduced-precision accumulation
         torch.backends.cuda.matmul.allow_tf32 = False
         torch.backends.cudnn.allow_tf32 = False
@@ -159,6 +166,30 @@ class CudaOps:
             self._scratch[device] = buf
         return buf
 
+    def _attn_lib(self, head_dim: int):
+        """The tensor-core attention library for this head size, built at first use."""
+        lib = self._attn_libs.get(head_dim)
+        if lib is None:
+            path = build_variant("attention_mma.cu", {"RV_HD": head_dim}, f"attn_hd{head_dim}",
+                                 verbose=self._verbose_build)
+            try:
+                lib = ctypes.CDLL(path)
+            except OSError as e:
+                raise KernelError(f"cannot load the kernel library {path}: {e}") from None
+            getattr(lib, f"rv_attention_mma_last_error_hd{head_dim}").restype = ctypes.c_char_p
+            self._attn_libs[head_dim] = lib
+        return lib
+
+    def _check_attn(self, lib, head_dim: int, rc: int, what: str) -> None:
+        self.launches += 1
+        if rc != 0:
+            msg = getattr(lib, f"rv_attention_mma_last_error_hd{head_dim}")().decode()
+            raise KernelError(f"{what}: {msg}")
+
+    @staticmethod
+    def _mma_ok(dtype, head_dim: int) -> bool:
+        return dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= 128
+
     def paged_attention(self, qkv, num_heads, num_kv_heads, head_dim, k_cache, v_cache,
                         ctx, group, scale, window, out):
         self._need(qkv, "query rows")
@@ -168,11 +199,28 @@ class CudaOps:
         code = _code(qkv.dtype)
         win = c_int(window if window else 0)
         nd = ctx.n_decode
+        mma = self._mma_ok(qkv.dtype, head_dim)
         if nd > 0:
-            self.paged_attention_decode(qkv, num_heads, num_kv_heads, head_dim, k_cache, v_cache,
-                                        group.block_table, ctx.ctx_lens, nd, ctx.max_ctx_len,
-                                        group.page_size, scale, window, out)
-        if ctx.n_tokens > nd:
+            if mma and self.decode_attention == "mma":
+                self.paged_attention_decode_mma(qkv, num_heads, num_kv_heads, head_dim, k_cache,
+                                                v_cache, group.block_table, ctx.q_start,
+                                                ctx.ctx_lens, nd, ctx.max_ctx_len,
+                                                group.page_size, scale, window, out)
+            else:
+                self.paged_attention_decode(qkv, num_heads, num_kv_heads, head_dim, k_cache,
+                                            v_cache, group.block_table, ctx.ctx_lens, nd,
+                                            ctx.max_ctx_len, group.page_size, scale, window, out)
+        if ctx.n_tokens > nd and mma and self.prefill_attention == "mma":
+            lib = self._attn_lib(head_dim)
+            fn = getattr(lib, f"rv_paged_attention_prefill_mma_hd{head_dim}")
+            self._check_attn(lib, head_dim, fn(
+                _ptr(qkv), c_int(qkv.shape[1]), _ptr(k_cache), _ptr(v_cache),
+                _ptr(group.block_table), c_int(group.max_blocks), _ptr(ctx.q_start),
+                _ptr(ctx.ctx_lens), _ptr(out), c_int(nd), c_int(ctx.n_reqs - nd),
+                c_int(ctx.max_q_len), c_int(num_heads), c_int(num_kv_heads),
+                c_int(group.page_size), c_float(scale), win, self._stream()),
+                "paged_attention_prefill_mma")
+        elif ctx.n_tokens > nd:
             self._check(self.lib.rv_paged_attention_warp(
                 _ptr(qkv), code, c_int(qkv.shape[1]), _ptr(k_cache), _ptr(v_cache),
                 _ptr(group.block_table), c_int(group.max_blocks), _ptr(ctx.q_start),
@@ -196,6 +244,29 @@ class CudaOps:
             c_int(n_reqs), c_int(max_ctx_len), c_int(num_heads), c_int(num_kv_heads),
             c_int(head_dim), c_int(page_size), c_float(scale), c_int(window if window else 0),
             self._stream()), "paged_attention_decode")
+
+    def paged_attention_decode_mma(self, qkv, num_heads, num_kv_heads, head_dim, k_cache, v_cache,
+                                   block_table, q_start, ctx_lens, n_reqs, max_ctx_len,
+                                   page_size, scale, window, out, scratch=None):
+        """Tensor-core split-KV attention (bfloat16) for requests [0, n_reqs) that bring one
+        token each; the splits are combined by the merge kernel."""
+        need = self.lib.rv_paged_attention_decode_scratch_bytes(
+            c_int(n_reqs), c_int(num_heads), c_int(head_dim), c_int(max_ctx_len))
+        if scratch is None:
+            scratch = self._scratch_buffer(need, qkv.device)
+        lib = self._attn_lib(head_dim)
+        fn = getattr(lib, f"rv_paged_attention_decode_mma_hd{head_dim}")
+        win = c_int(window if window else 0)
+        self._check_attn(lib, head_dim, fn(
+            _ptr(qkv), c_int(qkv.shape[1]), _ptr(k_cache), _ptr(v_cache), _ptr(block_table),
+            c_int(block_table.shape[1]), _ptr(q_start), _ptr(ctx_lens), _ptr(scratch),
+            c_longlong(scratch.numel() * scratch.element_size()), c_int(n_reqs),
+            c_int(max_ctx_len), c_int(num_heads), c_int(num_kv_heads), c_int(page_size),
+            c_float(scale), win, self._stream()), "paged_attention_decode_mma")
+        self._check(self.lib.rv_paged_attention_merge(
+            _ptr(scratch), _ptr(ctx_lens), _ptr(out), _code(out.dtype), c_int(n_reqs),
+            c_int(max_ctx_len), c_int(num_heads), c_int(head_dim), win, self._stream()),
+            "paged_attention_merge")
 
     def paged_attention_general(self, qkv, num_heads, num_kv_heads, head_dim, k_cache, v_cache,
                                 ctx, group, scale, window, out):

@@ -34,8 +34,13 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC",
 _lock = threading.Lock()
 
 
+# Sources compiled on demand with a size baked in, each into a library of its own.
+VARIANT_SOURCES = {"attention_mma.cu"}
+
+
 def sources() -> List[str]:
-    return sorted(f for f in os.listdir(CSRC) if f.endswith(".cu"))
+    return sorted(f for f in os.listdir(CSRC)
+                  if f.endswith(".cu") and f not in VARIANT_SOURCES)
 
 
 def find_nvcc() -> str:
@@ -122,6 +127,7 @@ def build(verbose: bool = True, force: bool = False) -> str:
             os.replace(tmp_out, out)
             for old in os.listdir(os.path.dirname(out)):       # libraries of older sources
                 if old.startswith("librvllm_b200_") and old.endswith(".so") and \
+                        old.count("_") == 2 and \
                         os.path.join(os.path.dirname(out), old) != out:
                     try:
                         os.remove(os.path.join(os.path.dirname(out), old))
@@ -129,5 +135,40 @@ def build(verbose: bool = True, force: bool = False) -> str:
                         pass
         finally:
             shutil.rmtree(work, ignore_errors=True)
+        _say(f"built {os.path.basename(out)} in {time.time() - t0:.0f} s", verbose)
+        return out
+
+
+def build_variant(source: str, defines: dict, tag: str, verbose: bool = True) -> str:
+    """Compile one of `VARIANT_SOURCES` with the given -D definitions into its own
+    library `librvllm_b200_<tag>_<hash>.so`; returns its path."""
+    with _lock:
+        h = hashlib.sha256()
+        for name in (source, "common.cuh"):
+            with open(os.path.join(CSRC, name), "rb") as f:
+                h.update(f.read())
+        flags = [f"-D{k}={v}" for k, v in sorted(defines.items())]
+        h.update(" ".join(ARCH_FLAGS + NVCC_FLAGS + flags).encode())
+        out = os.path.join(build_dir(), f"librvllm_b200_{tag}_{h.hexdigest()[:16]}.so")
+        if os.path.isfile(out):
+            return out
+        nvcc = find_nvcc()
+        t0 = time.time()
+        _say(f"compiling {source} for {tag} (first use of this size)", verbose)
+        tmp_out = out + f".{os.getpid()}.tmp"
+        cmd = [nvcc, *ARCH_FLAGS, *NVCC_FLAGS, *flags, "-I", CSRC, "-shared", "-o", tmp_out,
+               os.path.join(CSRC, source), "-lcudart"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise KernelError(f"nvcc failed on {source} ({tag}):\n{r.stderr[-4000:]}")
+        os.replace(tmp_out, out)
+        prefix = f"librvllm_b200_{tag}_"
+        for old in os.listdir(os.path.dirname(out)):
+            if old.startswith(prefix) and old.endswith(".so") and \
+                    os.path.join(os.path.dirname(out), old) != out:
+                try:
+                    os.remove(os.path.join(os.path.dirname(out), old))
+                except OSError:
+                    pass
         _say(f"built {os.path.basename(out)} in {time.time() - t0:.0f} s", verbose)
         return out
