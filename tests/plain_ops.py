@@ -69,7 +69,7 @@ class PlainOps:
             return x
 
         q = norm_rotate(_f(qkv[:, :qd]).reshape(n, num_heads, hd), q_weight)
-        qkv[:, :qd] = q.reshape(n, qd).to(qkv.dtype)
+        qkv[:, :qd] = q.reshape(n, qd).to(qkv.dtype).clone()
         if num_kv_heads:
             k = norm_rotate(_f(qkv[:, qd:qd + kd]).reshape(n, num_kv_heads, hd), k_weight)
             v = qkv[:, qd + kd:qd + 2 * kd].reshape(n, num_kv_heads, hd)
