@@ -304,6 +304,100 @@ def run_prefill_only(torch, fresh_runner, prompts, StepEntry):
     return 0
 
 
+def run_kernels(args):
+    """Single kernels at LFM2-1.2B sizes, timed as launches captured in one CUDA graph (no
+    host gaps), over operands larger than L2.  One JSON line."""
+    import math
+    from types import SimpleNamespace
+
+    import torch
+
+    from rvllm_b200.kernels import cuda_ops
+    ops = cuda_ops()
+    pk = peaks()
+    nh, nkv, hd, ps = 32, 8, 64, PAGE
+    out = {"only": "kernels", "peaks": pk["source"]}
+
+    def graph_time(fns, reps=5):
+        for f in fns[:2]:
+            f()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for f in fns:
+                f()
+        g.replay()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(reps):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            g.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1) * 1e3 / len(fns))
+        return sorted(ts)[len(ts) // 2]
+
+    if args.kernel in ("all", "attn_decode"):
+        B, ctx = args.kernel_batch, args.kernel_ctx
+        blocks = -(-ctx // ps)
+        layers = max(2, min(6, (400 << 20) // (B * ctx * nkv * hd * 4)))   # distinct caches > L2
+        caches = [(torch.randn(B * blocks, ps, nkv, hd, device="cuda", dtype=torch.bfloat16),
+                   torch.randn(B * blocks, ps, nkv, hd, device="cuda", dtype=torch.bfloat16))
+                  for _ in range(layers)]
+        table = torch.randperm(B * blocks, device="cuda").to(torch.int32).view(B, blocks)
+        q = torch.randn(B, (nh + 2 * nkv) * hd, device="cuda", dtype=torch.bfloat16)
+        o = torch.empty(B, nh * hd, device="cuda", dtype=torch.bfloat16)
+        cl = torch.full((B,), ctx, dtype=torch.int32, device="cuda")
+        qs = torch.arange(B + 1, dtype=torch.int32, device="cuda")
+        scale = 1 / math.sqrt(hd)
+        nbytes = B * ctx * nkv * hd * 2 * 2
+        for name, fn in (("mma", lambda k, v: ops.paged_attention_decode_mma(
+                q, nh, nkv, hd, k, v, table, qs, cl, B, ctx, ps, scale, None, o)),
+                         ("simt", lambda k, v: ops.paged_attention_decode(
+                q, nh, nkv, hd, k, v, table, cl, B, ctx, ps, scale, None, o))):
+            us = graph_time([(lambda k=k, v=v: fn(k, v)) for k, v in caches])
+            out[f"attn_decode_{name}_b{B}_ctx{ctx}"] = {
+                "us": round(us, 1), "GB/s": round(nbytes / us / 1e3, 1),
+                "frac_hbm": round(nbytes / us / 1e3 / pk["hbm_gbs"], 3)}
+    if args.kernel in ("all", "attn_prefill"):
+        T = PREFILL_TOKENS
+        blocks = -(-T // ps)
+        kc = torch.randn(blocks, ps, nkv, hd, device="cuda", dtype=torch.bfloat16)
+        vc = torch.randn_like(kc)
+        table = torch.randperm(blocks, device="cuda").to(torch.int32).view(1, blocks)
+        q = torch.randn(T, (nh + 2 * nkv) * hd, device="cuda", dtype=torch.bfloat16)
+        o = torch.empty(T, nh * hd, device="cuda", dtype=torch.bfloat16)
+        ctx = SimpleNamespace(n_tokens=T, n_reqs=1, n_decode=0, max_ctx_len=T, max_q_len=T,
+                              q_start=torch.tensor([0, T], dtype=torch.int32, device="cuda"),
+                              ctx_lens=torch.tensor([T], dtype=torch.int32, device="cuda"),
+                              token_req=torch.zeros(T, dtype=torch.int32, device="cuda"))
+        group = SimpleNamespace(block_table=table, max_blocks=blocks, page_size=ps, window=None)
+        us = graph_time([lambda: ops.paged_attention(q, nh, nkv, hd, kc, vc, ctx, group,
+                                                     1 / math.sqrt(hd), None, o)] * 4)
+        flops = 4 * nh * hd * T * (T + 1) / 2
+        out[f"attn_prefill_t{T}"] = {"us": round(us, 1), "TFLOP/s": round(flops / us / 1e6, 1),
+                                     "frac_bf16": round(flops / us / 1e6 / pk["bf16_tflops"], 3)}
+    if args.kernel in ("all", "gemm"):
+        M = 8
+        x = torch.randn(M, 8192, device="cuda", dtype=torch.bfloat16)
+        for N, K in ((6144, 2048), (2048, 2048), (3072, 2048), (16384, 2048), (2048, 8192),
+                     (65536, 2048)):
+            copies = max(4, min(48, (300 << 20) // (N * K * 2)))
+            ws = [torch.randn(N, K, device="cuda", dtype=torch.bfloat16) for _ in range(copies)]
+            xs = x[:, :K].contiguous()
+            t_lib = graph_time([(lambda w=w: torch.mm(xs, w.t())) for w in ws])
+            t_own = graph_time([(lambda w=w: ops.linear_tcgen05(xs, w, torch.bfloat16)) for w in ws])
+            out[f"gemm_m{M}_n{N}_k{K}"] = {
+                "cublas_us": round(t_lib, 1), "tcgen05_us": round(t_own, 1),
+                "tcgen05_GB/s": round(N * K * 2 / t_own / 1e3, 1),
+                "frac_hbm": round(N * K * 2 / t_own / 1e3 / pk["hbm_gbs"], 3)}
+            del ws
+        ops.check_status()
+    print(json.dumps(out))
+    return 0
+
+
 def run_reference(args):
     print(json.dumps({
         "impl": "reference",
@@ -319,8 +413,12 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "kernels"],
                     help="run one part only (for profiling); the JSON line then lacks the rest")
+    ap.add_argument("--kernel", default="all",
+                    help="with --only kernels: attn_decode, attn_prefill, gemm or all")
+    ap.add_argument("--kernel-batch", type=int, default=64)
+    ap.add_argument("--kernel-ctx", type=int, default=4096)
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -329,6 +427,8 @@ def main():
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.only == "kernels":
+        return run_kernels(args)
     return run_ours(args)
 
 

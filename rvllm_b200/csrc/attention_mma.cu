@@ -76,6 +76,7 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_attention_mma_kernel(
     const int* __restrict__ q_start, const int* __restrict__ ctx_lens, bf16* __restrict__ out,
     float* __restrict__ part_o, float2* __restrict__ part_ml, int max_splits, int first_req,
     int num_heads, int num_kv_heads, int page_size, float scale_log2, int window) {
+    rv_pdl_prologue();
     constexpr int BM = 16 * NWARPS;
     constexpr int LD = HD + 8;          // padded row: conflict-free ldmatrix for HD % 16 == 0
     constexpr int CPR = HD / 8;         // 16-byte chunks per row
@@ -117,6 +118,7 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_attention_mma_kernel(
     const int tile_begin = key_lo / RV_BN, tile_end = key_hi / RV_BN;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int page_shift = (page_size & (page_size - 1)) == 0 ? 31 - __clz(page_size) : -1;
     const int* table = block_table + (size_t)r * max_blocks;
     const size_t kv_row = (size_t)num_kv_heads * HD;
 
@@ -129,19 +131,36 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_attention_mma_kernel(
         const bf16* src = q + (size_t)(qs + tok) * q_stride + (size_t)(g * G + hg) * HD + ch * 8;
         cp_async_16(Qs + m * LD + ch * 8, src, valid);
     }
+    // Each thread copies the same few rows of every tile: ROWS rows, one 16-byte chunk of K
+    // and of V each.  The page lookups of a tile are all issued before the first copy, so
+    // they overlap instead of forming a chain of dependent loads.
+    constexpr int ROWS = RV_BN * CPR / (NWARPS * 32) > 0 ? (RV_BN * CPR + NWARPS * 32 - 1) / (NWARPS * 32) : 1;
     auto load_tile = [&](int t, int stage) {
         bf16* kd = Ks + stage * RV_BN * LD;
         bf16* vd = Vs + stage * RV_BN * LD;
-        for (int c = tid; c < RV_BN * CPR; c += NWARPS * 32) {
-            const int row = c / CPR, ch = c - row * CPR;
+        size_t off[ROWS];
+        bool valid[ROWS];
+#pragma unroll
+        for (int i = 0; i < ROWS; ++i) {
+            const int c = tid + i * NWARPS * 32;
+            const int row = c / CPR;
             const int j = t * RV_BN + row;
             int page = -1;
-            if (j < clen) page = table[j / page_size];
-            const bool valid = page >= 0;
-            const size_t off = valid ? ((size_t)page * page_size + j % page_size) * kv_row +
-                                           (size_t)g * HD + ch * 8 : 0;
-            cp_async_16(kd + row * LD + ch * 8, k_cache + off, valid);
-            cp_async_16(vd + row * LD + ch * 8, v_cache + off, valid);
+            if (c < RV_BN * CPR && j < clen)
+                page = table[page_shift >= 0 ? (j >> page_shift) : (j / page_size)];
+            valid[i] = page >= 0;
+            const int in_page = page_shift >= 0 ? (j & (page_size - 1)) : (j % page_size);
+            off[i] = valid[i] ? ((size_t)page * page_size + in_page) * kv_row + (size_t)g * HD +
+                                    (c - row * CPR) * 8 : 0;
+        }
+#pragma unroll
+        for (int i = 0; i < ROWS; ++i) {
+            const int c = tid + i * NWARPS * 32;
+            if (c < RV_BN * CPR) {
+                const int row = c / CPR, ch = c - row * CPR;
+                cp_async_16(kd + row * LD + ch * 8, k_cache + off[i], valid[i]);
+                cp_async_16(vd + row * LD + ch * 8, v_cache + off[i], valid[i]);
+            }
         }
     };
     load_tile(tile_begin, 0);
@@ -339,7 +358,7 @@ extern "C" int RV_SYM(rv_paged_attention_prefill_mma)(
         configured = true;
     }
     dim3 grid((unsigned)tiles, num_kv_heads, n_reqs);
-    paged_attention_mma_kernel<RV_HD, 4, false><<<grid, 128, smem, (cudaStream_t)stream>>>(
+    rv_launch(paged_attention_mma_kernel<RV_HD, 4, false>, dim3(grid), dim3(128), smem, (cudaStream_t)stream, 
         (const bf16*)q, q_stride, (const bf16*)k_cache, (const bf16*)v_cache, block_table,
         max_blocks, q_start, ctx_lens, (bf16*)out, nullptr, nullptr, 0, first_req, num_heads,
         num_kv_heads, page_size, scale * 1.4426950408889634f, window);
@@ -380,7 +399,7 @@ extern "C" int RV_SYM(rv_paged_attention_decode_mma)(
     dim3 grid(max_splits, num_kv_heads * tiles_per_head, n_reqs);
     float* part_o = (float*)scratch;
     float2* part_ml = (float2*)((char*)scratch + slots * RV_HD * 4);
-    paged_attention_mma_kernel<RV_HD, 1, true><<<grid, 32, smem, (cudaStream_t)stream>>>(
+    rv_launch(paged_attention_mma_kernel<RV_HD, 1, true>, dim3(grid), dim3(32), smem, (cudaStream_t)stream, 
         (const bf16*)q, q_stride, (const bf16*)k_cache, (const bf16*)v_cache, block_table,
         max_blocks, q_start, ctx_lens, nullptr, part_o, part_ml, max_splits, 0, num_heads,
         num_kv_heads, page_size, scale * 1.4426950408889634f, window);

@@ -63,6 +63,7 @@ __global__ void paged_attention_warp_kernel(
     const int* __restrict__ q_start, const int* __restrict__ ctx_lens,
     const int* __restrict__ token_req, T* __restrict__ out, int first_token, int n_tokens,
     int num_heads, int num_kv_heads, int hd, int page_size, float scale, int window) {
+    rv_pdl_prologue();
     constexpr bool kFast = sizeof(T) == 2;
     extern __shared__ float q_smem[];   // [warps per block][hd]
     const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
@@ -139,6 +140,7 @@ __global__ void __launch_bounds__(128) paged_attention_decode_kernel(
     const int* __restrict__ ctx_lens, float* __restrict__ part_o, float2* __restrict__ part_ml,
     int max_splits, int num_heads, int num_kv_heads, int hd, int page_size, float scale,
     int window) {
+    rv_pdl_prologue();
     constexpr bool kFast = sizeof(T) == 2;
     constexpr int GT = RV_ATTN_GT;
     extern __shared__ float smem[];
@@ -270,6 +272,7 @@ __global__ void paged_attention_merge_kernel(const float* __restrict__ part_o,
                                              const float2* __restrict__ part_ml,
                                              const int* __restrict__ ctx_lens, T* __restrict__ out,
                                              int max_splits, int num_heads, int hd, int window) {
+    rv_pdl_prologue();
     constexpr bool kFast = sizeof(T) == 2;
     const int r = blockIdx.y, h = blockIdx.x;
     const int clen = ctx_lens[r];
@@ -333,7 +336,7 @@ extern "C" int rv_paged_attention_warp(const void* q, int dtype, int q_stride, c
     const size_t smem = (size_t)wpb * hd * sizeof(float);
     cudaStream_t s = (cudaStream_t)stream;
     RV_DISPATCH_DTYPE(dtype, "paged_attention",
-        RV_DISPATCH_DPL(hd, (paged_attention_warp_kernel<T, DPL><<<(int)blocks, wpb * 32, smem, s>>>(
+        RV_DISPATCH_DPL(hd, (rv_launch(paged_attention_warp_kernel<T, DPL>, dim3((int)blocks), dim3(wpb * 32), smem, s, 
             (const T*)q, q_stride, (const T*)k_cache, (const T*)v_cache, block_table, max_blocks,
             q_start, ctx_lens, token_req, (T*)out, first_token, n_tokens, num_heads, num_kv_heads,
             hd, page_size, scale, window))));
@@ -375,14 +378,14 @@ extern "C" int rv_paged_attention_decode(const void* q, int dtype, int q_stride,
                                  4 * RV_ATTN_GT * (hd + 2)) * sizeof(float);
     cudaStream_t s = (cudaStream_t)stream;
     RV_DISPATCH_DTYPE(dtype, "paged_attention_decode",
-        RV_DISPATCH_DPL(hd, (paged_attention_decode_kernel<T, DPL><<<grid, 128, smem, s>>>(
+        RV_DISPATCH_DPL(hd, (rv_launch(paged_attention_decode_kernel<T, DPL>, dim3(grid), dim3(128), smem, s, 
             (const T*)q, q_stride, (const T*)k_cache, (const T*)v_cache, block_table, max_blocks,
             ctx_lens, part_o, part_ml, max_splits, num_heads, num_kv_heads, hd, page_size, scale,
             window))));
     RV_CHECK_LAUNCH("paged_attention_decode");
     dim3 mgrid(num_heads, n_reqs);
     RV_DISPATCH_DTYPE(dtype, "paged_attention_merge",
-        (paged_attention_merge_kernel<T><<<mgrid, hd < 32 ? 32 : (hd > 128 ? 128 : ((hd + 31) / 32) * 32), 0, s>>>(
+        (rv_launch(paged_attention_merge_kernel<T>, dim3(mgrid), dim3(hd < 32 ? 32 : (hd > 128 ? 128 : ((hd + 31) / 32) * 32)), 0, s, 
             part_o, part_ml, ctx_lens, (T*)out, max_splits, num_heads, hd, window)));
     RV_CHECK_LAUNCH("paged_attention_merge");
     return 0;
@@ -404,7 +407,7 @@ extern "C" int rv_paged_attention_merge(const void* scratch, const int* ctx_lens
     dim3 mgrid(num_heads, n_reqs);
     const int threads = hd < 32 ? 32 : (hd > 128 ? 128 : ((hd + 31) / 32) * 32);
     RV_DISPATCH_DTYPE(dtype, "paged_attention_merge",
-        (paged_attention_merge_kernel<T><<<mgrid, threads, 0, (cudaStream_t)stream>>>(
+        (rv_launch(paged_attention_merge_kernel<T>, dim3(mgrid), dim3(threads), 0, (cudaStream_t)stream, 
             part_o, part_ml, ctx_lens, (T*)out, max_splits, num_heads, hd, window)));
     RV_CHECK_LAUNCH("paged_attention_merge");
     return 0;

@@ -9,6 +9,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #define RV_DTYPE_F32 0
 #define RV_DTYPE_BF16 1
@@ -83,4 +84,44 @@ __device__ __forceinline__ float rv_block_max(float v, float* scratch) {
     }
     __syncthreads();
     return scratch[32];
+}
+
+// ---- programmatic dependent launch -------------------------------------------------------
+// Every kernel of this library is launched with the programmatic-stream-serialization
+// attribute and begins with `rv_pdl_prologue()`: it lets the next kernel of the stream
+// start (and run whatever it does before its own wait, e.g. the matrix product's copies
+// of weight tiles), then waits until the previous kernel has completed and its writes
+// are visible.  Nothing is read from or written to global memory before the wait except
+// constant weights.  RVLLM_PDL=0 turns the attribute off (the two instructions are then
+// no-ops).
+__device__ __forceinline__ void rv_pdl_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::);
+}
+__device__ __forceinline__ void rv_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void rv_pdl_prologue() {
+    rv_pdl_launch_dependents();
+    rv_pdl_wait();
+}
+static inline int rv_pdl_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("RVLLM_PDL");
+        v = (e && e[0] == '0') ? 0 : 1;
+    }
+    return v;
+}
+template <typename... KArgs, typename... Args>
+static inline void rv_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                             cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = rv_pdl_enabled();
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }

@@ -13,17 +13,41 @@ void rv_set_error(const char* fmt, ...) {
     va_end(ap);
 }
 
+__device__ __forceinline__ float4 rv_load4(const float* p) { return *(const float4*)p; }
+__device__ __forceinline__ float4 rv_load4(const __nv_bfloat16* p) {
+    const uint2 raw = *(const uint2*)p;
+    const float2 a = __bfloat1622float2(*(const __nv_bfloat162*)&raw.x);
+    const float2 b = __bfloat1622float2(*(const __nv_bfloat162*)&raw.y);
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void rv_store4(float* p, float4 v) { *(float4*)p = v; }
+__device__ __forceinline__ void rv_store4(__nv_bfloat16* p, float4 v) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 raw;
+    raw.x = *(const unsigned*)&a;
+    raw.y = *(const unsigned*)&b;
+    *(uint2*)p = raw;
+}
+
 // ---------------------------------------------------------------------------------
 // Embedding gather: out[t, :] = table[ids[t], :] (* scale), float32 out.
 // Reference counterpart: embed_lookup.cu (one thread per element, float32 table).
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                              float* __restrict__ out, int hidden, int vocab, float scale) {
+    rv_pdl_prologue();
     const int t = blockIdx.x;
     int id = ids[t];
     id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
     const T* row = table + (size_t)id * hidden;
     float* o = out + (size_t)t * hidden;
+    if (hidden % 4 == 0 && ((uintptr_t)table % 16 == 0) && ((uintptr_t)out % 16 == 0)) {
+        for (int i = threadIdx.x; i < hidden / 4; i += blockDim.x) {
+            const float4 v = rv_load4(row + 4 * i);
+            rv_store4(o + 4 * i, make_float4(v.x * scale, v.y * scale, v.z * scale, v.w * scale));
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = rv_load(row + i) * scale;
 }
 
@@ -32,7 +56,7 @@ extern "C" int rv_embed(const void* table, int dtype, const int* ids, float* out
     if (n_tokens == 0) return 0;
     if (n_tokens < 0 || hidden <= 0 || vocab <= 0) RV_FAIL("embed: bad sizes");
     RV_DISPATCH_DTYPE(dtype, "embed",
-                      (embed_kernel<T><<<n_tokens, 256, 0, (cudaStream_t)stream>>>(
+                      (rv_launch(embed_kernel<T>, dim3(n_tokens), dim3(hidden >= 2048 ? 512 : 256), 0, (cudaStream_t)stream, 
                           (const T*)table, ids, out, hidden, vocab, scale)));
     RV_CHECK_LAUNCH("embed");
     return 0;
@@ -49,6 +73,7 @@ template <typename TD, typename TO>
 __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta,
                                    const float* __restrict__ weight, TO* __restrict__ out,
                                    const int* __restrict__ rows, int hidden, float eps) {
+    rv_pdl_prologue();
     extern __shared__ float row[];
     __shared__ float scratch[33];
     const int m = blockIdx.x;
@@ -67,10 +92,72 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restri
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) rv_store(o + i, row[i] / rms * weight[i]);
 }
 
+// The same for widths that are a multiple of 4 and at most 16384: every thread keeps up
+// to four 4-element chunks of the row in registers, so each global value is loaded once
+// with a 16-byte (float32) or 8-byte (bfloat16) access and all loads are in flight together.
+template <typename TD, typename TO, int CHUNKS>
+__global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const TD* __restrict__ delta,
+                                       const float* __restrict__ weight, TO* __restrict__ out,
+                                       const int* __restrict__ rows, int hidden, float eps) {
+    rv_pdl_prologue();
+    __shared__ float scratch[33];
+    const int m = blockIdx.x;
+    const size_t in = (size_t)(rows ? rows[m] : m) * hidden;
+    const int nvec = hidden >> 2;
+    float4 x[CHUNKS], w[CHUNKS];
+    float ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+        const int i = threadIdx.x + c * blockDim.x;
+        if (i < nvec) {
+            x[c] = rv_load4(resid + in + 4 * i);
+            w[c] = rv_load4(weight + 4 * i);
+            if (delta) {
+                const float4 d = rv_load4(delta + in + 4 * i);
+                x[c].x += d.x; x[c].y += d.y; x[c].z += d.z; x[c].w += d.w;
+                if (!rows) rv_store4(resid + in + 4 * i, x[c]);
+            }
+            ss += x[c].x * x[c].x + x[c].y * x[c].y + x[c].z * x[c].z + x[c].w * x[c].w;
+        }
+    }
+    const float total = rv_block_sum(ss, scratch);
+    const float rms = sqrtf(total / (float)hidden + eps);
+    TO* o = out + (size_t)m * hidden;
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+        const int i = threadIdx.x + c * blockDim.x;
+        if (i < nvec)
+            rv_store4(o + 4 * i, make_float4(x[c].x / rms * w[c].x, x[c].y / rms * w[c].y,
+                                             x[c].z / rms * w[c].z, x[c].w / rms * w[c].w));
+    }
+}
+
 template <typename TD, typename TO>
 static int add_rmsnorm_launch(float* resid, const void* delta, const float* weight, void* out,
                               const int* rows, int n_rows, int hidden, float eps,
                               cudaStream_t stream) {
+    const bool aligned = ((uintptr_t)resid % 16 == 0) && ((uintptr_t)weight % 16 == 0) &&
+                         ((uintptr_t)out % 16 == 0) && (!delta || (uintptr_t)delta % 16 == 0);
+    if (hidden % 4 == 0 && hidden <= 16384 && aligned) {
+        const int nvec = hidden / 4;
+        int threads = ((nvec + 31) / 32) * 32;
+        int chunks = 1;
+        while (threads > 1024 || (chunks < 4 && threads > 512 && nvec > 512)) {
+            chunks *= 2;
+            threads = (((nvec + chunks - 1) / chunks + 31) / 32) * 32;
+        }
+        if (chunks == 1)
+            rv_launch(add_rmsnorm_vec_kernel<TD, TO, 1>, dim3(n_rows), dim3(threads), 0, stream, 
+                resid, (const TD*)delta, weight, (TO*)out, rows, hidden, eps);
+        else if (chunks == 2)
+            rv_launch(add_rmsnorm_vec_kernel<TD, TO, 2>, dim3(n_rows), dim3(threads), 0, stream, 
+                resid, (const TD*)delta, weight, (TO*)out, rows, hidden, eps);
+        else
+            rv_launch(add_rmsnorm_vec_kernel<TD, TO, 4>, dim3(n_rows), dim3(threads), 0, stream, 
+                resid, (const TD*)delta, weight, (TO*)out, rows, hidden, eps);
+        RV_CHECK_LAUNCH("add_rmsnorm");
+        return 0;
+    }
     const size_t smem = (size_t)hidden * sizeof(float);
     if (smem > 200 * 1024) RV_FAIL("add_rmsnorm: width %d exceeds the shared-memory row", hidden);
     if (smem > 48 * 1024) {
@@ -79,7 +166,7 @@ static int add_rmsnorm_launch(float* resid, const void* delta, const float* weig
         if (e != cudaSuccess) RV_FAIL("add_rmsnorm: %s", cudaGetErrorString(e));
     }
     const int threads = hidden >= 1024 ? 256 : 128;
-    add_rmsnorm_kernel<TD, TO><<<n_rows, threads, smem, stream>>>(
+    rv_launch(add_rmsnorm_kernel<TD, TO>, dim3(n_rows), dim3(threads), smem, stream, 
         resid, (const TD*)delta, weight, (TO*)out, rows, hidden, eps);
     RV_CHECK_LAUNCH("add_rmsnorm");
     return 0;
@@ -110,6 +197,7 @@ extern "C" int rv_add_rmsnorm(float* resid, const void* delta, int delta_dtype, 
 // Reference counterpart: silu_gate_multiply.cu (two separate inputs).
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ in, T* __restrict__ out, int ffn, size_t total) {
+    rv_pdl_prologue();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (size_t)gridDim.x * blockDim.x) {
         const size_t n = i / ffn;
@@ -123,6 +211,7 @@ __global__ void swiglu_kernel(const T* __restrict__ in, T* __restrict__ out, int
 // bfloat16, 8 elements per thread (16-byte loads); needs ffn % 8 == 0.
 __global__ void swiglu_bf16x8_kernel(const uint4* __restrict__ in, uint4* __restrict__ out,
                                      int ffn8, size_t total8) {
+    rv_pdl_prologue();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total8;
          i += (size_t)gridDim.x * blockDim.x) {
         const size_t n = i / ffn8;
@@ -150,11 +239,11 @@ extern "C" int rv_swiglu(const void* in, void* out, int dtype, int n_rows, int f
         ((uintptr_t)out % 16 == 0)) {
         const size_t total8 = total / 8;
         const int blocks = (int)((total8 + 255) / 256 < 148 * 16 ? (total8 + 255) / 256 : 148 * 16);
-        swiglu_bf16x8_kernel<<<blocks, 256, 0, s>>>((const uint4*)in, (uint4*)out, ffn / 8, total8);
+        rv_launch(swiglu_bf16x8_kernel, dim3(blocks), dim3(256), 0, s, (const uint4*)in, (uint4*)out, ffn / 8, total8);
     } else {
         const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
         RV_DISPATCH_DTYPE(dtype, "swiglu",
-                          (swiglu_kernel<T><<<blocks, 256, 0, s>>>((const T*)in, (T*)out, ffn, total)));
+                          (rv_launch(swiglu_kernel<T>, dim3(blocks), dim3(256), 0, s, (const T*)in, (T*)out, ffn, total)));
     }
     RV_CHECK_LAUNCH("swiglu");
     return 0;
@@ -165,6 +254,7 @@ extern "C" int rv_swiglu(const void* in, void* out, int dtype, int n_rows, int f
 template <typename T>
 __global__ void add_bias_kernel(T* __restrict__ x, const float* __restrict__ bias, int width,
                                 size_t total) {
+    rv_pdl_prologue();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (size_t)gridDim.x * blockDim.x)
         rv_store(x + i, rv_load(x + i) + bias[i % width]);
@@ -177,7 +267,7 @@ extern "C" int rv_add_bias(void* x, int dtype, const float* bias, int n_rows, in
     const size_t total = (size_t)n_rows * width;
     const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
     RV_DISPATCH_DTYPE(dtype, "add_bias",
-                      (add_bias_kernel<T><<<blocks, 256, 0, (cudaStream_t)stream>>>(
+                      (rv_launch(add_bias_kernel<T>, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, 
                           (T*)x, bias, width, total)));
     RV_CHECK_LAUNCH("add_bias");
     return 0;

@@ -1,0 +1,403 @@
+// Weight-streaming matrix product for few tokens on the 5th-generation tensor cores:
+//   y[M, N] = x[M, K] . W[N, K]^T,  bfloat16 operands, float32 accumulation,
+// for M <= 256 tokens (decode steps and short prompt portions), where the product is
+// bound by reading W once from HBM.
+//
+// The roles are swapped with respect to the usual orientation: 128 rows of W are the M
+// side of a tcgen05.mma (cta_group::1, M = 128, kind::f16) and the tokens, padded to a
+// multiple of 16, are its N side, so one instruction covers 128 output columns for all
+// tokens and the accumulator [128 lanes x tokens] lives in TMEM.  Operands reach shared
+// memory by TMA (cp.async.bulk.tensor.2d, 128-byte swizzle, K-major tiles of 64
+// elements) through a ring of stages guarded by mbarriers; one elected thread issues the
+// copies, one issues the MMAs (four K = 16 steps per stage), tcgen05.commit hands a
+// stage back to the producer, and after the last stage the four warps read the
+// accumulator with tcgen05.ld and write y.  The K range is split over the blocks of a
+// thread-block cluster (1, 2, 4 or 8 of them) so that every SM streams a share of W; each
+// block parks its float32 partial tile in its own shared memory, the cluster meets at a
+// barrier, and block r adds, for the tokens t = r mod size, the partial rows of all blocks
+// in rank order through distributed shared memory (no atomics, no global workspace: the
+// sum is deterministic).  The TMA copies are per block: no multicast.
+//
+// Every wait on an mbarrier is bounded: after RV_SPIN_LIMIT failed polls the thread
+// records an error code in `status`, every role leaves its loop, the producer waits
+// (again bounded) for the copies it has in flight, TMEM is freed and the block returns.
+//
+// Reference counterpart: `linear_f16` = cublasGemmEx (src/cuda/cublas_ops.rs:44-92).
+// Plain reference: tests/plain_ops.py linear.
+#include <cuda.h>
+
+#include "common.cuh"
+
+#define RV_GEMM_BM 128          // rows of W per block (the MMA's M)
+#define RV_GEMM_BK 64           // K elements per stage: 128 bytes, one swizzle row
+#define RV_GEMM_MAX_STAGES 6
+#define RV_GEMM_SMEM_LIMIT (226 * 1024)
+#define RV_SPIN_LIMIT (1u << 22)
+
+typedef __nv_bfloat16 bf16;
+
+// ---- PTX wrappers ---------------------------------------------------------------------
+__device__ __forceinline__ unsigned smem_u32(const void* p) {
+    return (unsigned)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+                 "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned parity) {
+    unsigned done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+// Bounded wait: false when the limit ran out or another thread already gave up.
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity,
+                                          volatile int* failed) {
+    for (unsigned i = 0; i < RV_SPIN_LIMIT; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (*failed) return false;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map,
+                                            unsigned long long* bar, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"((unsigned long long)map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+        : "memory");
+}
+__device__ __forceinline__ void tcgen05_commit(unsigned long long* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                 ::"r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void tcgen05_mma_f16(unsigned tmem_d, unsigned long long a_desc,
+                                                unsigned long long b_desc, unsigned idesc,
+                                                unsigned accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+        ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_load_16(unsigned taddr, unsigned (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, "
+        "%12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of 128
+// bytes, groups of 8 rows 1024 bytes apart (stride byte offset), leading byte offset
+// unused (1), descriptor version 1, layout type 2 (SWIZZLE_128B).
+__device__ __forceinline__ unsigned long long smem_desc_sw128(const void* tile) {
+    const unsigned long long addr = (smem_u32(tile) & 0x3FFFFu) >> 4;
+    return addr | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+
+// ---- the kernel -----------------------------------------------------------------------
+// grid (n_tiles, splits) with clusters of (1, splits); block 128 threads.
+// status[0]: first error code (0 = none).
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_cluster_f32(const float* local, unsigned rank) {
+    unsigned remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(local)), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+
+template <typename TO>
+__global__ void __launch_bounds__(128) gemm_tcgen05_kernel(
+    const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+    TO* __restrict__ out, int* __restrict__ status, int M, int N, int kblocks, int n_pad,
+    int stages) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    // the dynamic segment is aligned by hand: swizzled tiles need 1024-byte alignment
+    unsigned char* base = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const int w_bytes = RV_GEMM_BM * RV_GEMM_BK * 2;
+    const int x_bytes = n_pad * RV_GEMM_BK * 2;
+    unsigned char* w_tiles = base;
+    unsigned char* x_tiles = base + stages * w_bytes;
+    __shared__ __align__(8) unsigned long long full_bar[RV_GEMM_MAX_STAGES];
+    __shared__ __align__(8) unsigned long long empty_bar[RV_GEMM_MAX_STAGES];
+    __shared__ __align__(8) unsigned long long accum_bar;
+    __shared__ unsigned tmem_base_smem;
+    __shared__ volatile int failed;
+
+    // The next kernel of the stream may start its own preamble now.  This kernel's wait
+    // for the previous one comes later: W does not depend on it, only x and y do.
+    rv_pdl_launch_dependents();
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tile = blockIdx.x, split = blockIdx.y, splits = gridDim.y;
+    const int kb0 = (int)((long long)kblocks * split / splits);
+    const int kb1 = (int)((long long)kblocks * (split + 1) / splits);
+    const int nkb = kb1 - kb0;
+    unsigned tmem_cols = 32;
+    while ((int)tmem_cols < n_pad) tmem_cols <<= 1;
+
+    if (tid == 0) {
+        failed = 0;
+        for (int s = 0; s < stages; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        mbar_init(&accum_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(&tmem_base_smem)), "r"(tmem_cols));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const unsigned tmem_base = tmem_base_smem;
+
+    if (warp == 0 && lane == 0) {
+        // ---- producer: TMA copies of W and x tiles ------------------------------------
+        const unsigned tx = (unsigned)(w_bytes + x_bytes);
+        // fill the ring with weight tiles before waiting for the previous kernel: they
+        // stream from HBM while it is still running
+        const int pre = min(nkb, stages);
+        for (int i = 0; i < pre; ++i) {
+            mbar_expect_tx(&full_bar[i], tx);
+            tma_load_2d(w_tiles + i * w_bytes, &map_w, &full_bar[i], (kb0 + i) * RV_GEMM_BK,
+                        tile * RV_GEMM_BM);
+        }
+        rv_pdl_wait();
+        for (int i = 0; i < pre; ++i)
+            tma_load_2d(x_tiles + i * x_bytes, &map_x, &full_bar[i], (kb0 + i) * RV_GEMM_BK, 0);
+        int issued = pre;
+        for (int i = pre; i < nkb; ++i) {
+            const int s = i % stages;
+            {
+                const unsigned parity = ((i / stages) - 1) & 1;
+                if (!mbar_wait(&empty_bar[s], parity, &failed)) {
+                    if (!failed) { failed = 1; atomicCAS(status, 0, 1); }
+                    break;
+                }
+            }
+            mbar_expect_tx(&full_bar[s], tx);
+            tma_load_2d(w_tiles + s * w_bytes, &map_w, &full_bar[s], (kb0 + i) * RV_GEMM_BK,
+                        tile * RV_GEMM_BM);
+            tma_load_2d(x_tiles + s * x_bytes, &map_x, &full_bar[s], (kb0 + i) * RV_GEMM_BK, 0);
+            issued = i + 1;
+        }
+        // no copy of this block may still be in flight when it returns
+        for (int i = max(0, issued - stages); i < issued; ++i) {
+            const int s = i % stages;
+            bool ok = false;
+            for (unsigned n = 0; n < RV_SPIN_LIMIT && !ok; ++n)
+                ok = mbar_try_wait(&full_bar[s], (i / stages) & 1);
+            if (!ok && !failed) { failed = 1; atomicCAS(status, 0, 2); }
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---- MMA issuer -------------------------------------------------------------------
+        rv_pdl_wait();     // the bounded waits below start only when the previous kernel is done
+        // instruction descriptor: D float32, A and B bfloat16, both K-major, N = n_pad, M = 128
+        const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) |
+                               ((unsigned)(n_pad >> 3) << 17) | ((unsigned)(RV_GEMM_BM >> 4) << 24);
+        for (int i = 0; i < nkb; ++i) {
+            const int s = i % stages;
+            if (!mbar_wait(&full_bar[s], (i / stages) & 1, &failed)) {
+                if (!failed) { failed = 1; atomicCAS(status, 0, 3); }
+                break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const unsigned long long a0 = smem_desc_sw128(w_tiles + s * w_bytes);
+            const unsigned long long b0 = smem_desc_sw128(x_tiles + s * x_bytes);
+#pragma unroll
+            for (int k = 0; k < RV_GEMM_BK / 16; ++k)      // 32 bytes per K = 16 step
+                tcgen05_mma_f16(tmem_base, a0 + 2 * k, b0 + 2 * k, idesc, (i | k) != 0);
+            tcgen05_commit(&empty_bar[s]);                  // frees the stage when the MMAs are done
+        }
+        tcgen05_commit(&accum_bar);                         // arrives when every MMA above is done
+    }
+    __syncwarp();
+    rv_pdl_wait();            // before any thread writes y: the previous kernel is done
+
+    // ---- epilogue: all four warps, warp w owns TMEM lanes [32w, 32w + 32) -------------------
+    bool have = mbar_wait(&accum_bar, 0, &failed);
+    if (!have && !failed) { failed = 1; atomicCAS(status, 0, 4); }
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    __syncthreads();          // `failed` is final; the producer has drained its copies
+    const bool good = !failed;
+    const int n_local = warp * 32 + lane;
+    const int n = tile * RV_GEMM_BM + n_local;                // this thread's output column
+    float* park = (float*)base;                               // [token][128], over the stage ring
+    for (int c = 0; c < n_pad; c += 16) {
+        unsigned r[16];
+        tmem_load_16(tmem_base + ((unsigned)(warp * 32) << 16) + (unsigned)c, r);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const int t = c + j;
+            if (t < M) {
+                const float v = good ? __uint_as_float(r[j]) : 0.f;
+                if (splits == 1) {
+                    if (n < N && good) rv_store(out + (size_t)t * N + n, v);
+                } else {
+                    park[t * RV_GEMM_BM + n_local] = v;
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                     "r"(tmem_cols));
+    }
+    if (splits == 1) return;
+
+    // ---- every block of the cluster adds its share of token rows, in rank order ----------
+    cluster_sync_all();                                       // all partial tiles are parked
+    if (n < N) {
+        for (int t = split; t < M; t += splits) {
+            float acc = 0.f;
+            for (int s = 0; s < splits; ++s)
+                acc += ld_cluster_f32(park + t * RV_GEMM_BM + n_local, (unsigned)s);
+            rv_store(out + (size_t)t * N + n, acc);
+        }
+    }
+    cluster_sync_all();                                       // nobody leaves while it is read
+}
+
+// ---- host side ----------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) ==
+                cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// A [rows, K] bfloat16 row-major matrix seen through boxes of [box_rows, 64].
+static int make_map(CUtensorMap* map, const void* ptr, long long rows, long long K, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) RV_FAIL("gemm_tcgen05: cuTensorMapEncodeTiled is not available in this driver");
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+    cuuint32_t box[2] = {RV_GEMM_BK, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides,
+                    box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) RV_FAIL("gemm_tcgen05: cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return 0;
+}
+
+// How many blocks share the K range of one tile: a power of two up to 8 (the portable
+// cluster size), enough that about 148 blocks or more stream W, and at least four stages
+// of work each.  Depends on N and K only, so a row's sum order does not depend on M.
+extern "C" int rv_gemm_tcgen05_splits(int N, int K) {
+    const int tiles = (N + RV_GEMM_BM - 1) / RV_GEMM_BM;
+    const int kblocks = (K + RV_GEMM_BK - 1) / RV_GEMM_BK;
+    int s = 1;
+    while (s < 8 && tiles * s < 148 && kblocks / (2 * s) >= 4) s *= 2;
+    return s;
+}
+
+static int pick_stages(int n_pad) {
+    const int per_stage = RV_GEMM_BM * RV_GEMM_BK * 2 + n_pad * RV_GEMM_BK * 2;
+    int st = (RV_GEMM_SMEM_LIMIT - 1024) / per_stage;
+    return st > RV_GEMM_MAX_STAGES ? RV_GEMM_MAX_STAGES : st;
+}
+
+// Once per process, outside any stream capture: raise the kernels' shared-memory limit and
+// look up the driver's tensor-map encoder.
+extern "C" int rv_gemm_tcgen05_init() {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<bf16>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         RV_GEMM_SMEM_LIMIT);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(gemm_tcgen05_kernel<float>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, RV_GEMM_SMEM_LIMIT);
+    if (e != cudaSuccess) RV_FAIL("gemm_tcgen05: %s", cudaGetErrorString(e));
+    if (!encode_fn()) RV_FAIL("gemm_tcgen05: cuTensorMapEncodeTiled is not available in this driver");
+    return 0;
+}
+
+template <typename TO>
+static int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, void* out, int* status, int M,
+                  int N, int kblocks, int n_pad, int stages, int tiles, int splits, size_t smem,
+                  cudaStream_t stream) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(tiles, splits, 1);
+    cfg.blockDim = dim3(128, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = splits;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = rv_pdl_enabled();
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<TO>, map_w, map_x, (TO*)out, status,
+                                       M, N, kblocks, n_pad, stages);
+    if (e != cudaSuccess) RV_FAIL("gemm_tcgen05: %s", cudaGetErrorString(e));
+    return 0;
+}
+
+// y = x . W^T.  `status` is a device int the kernel sets to a non-zero code if a bounded
+// wait ran out (1: producer waiting for a free stage, 2: copies still in flight at exit,
+// 3: MMA issuer waiting for data, 4: epilogue waiting for the accumulator).
+extern "C" int rv_gemm_tcgen05(const void* x, const void* w, void* out, int out_dtype, int* status,
+                               int M, int N, int K, void* stream) {
+    if (M == 0) return 0;
+    if (M < 0 || M > 256 || N <= 0 || K <= 0)
+        RV_FAIL("gemm_tcgen05: sizes out of range (M = %d must be 1..256, N = %d, K = %d)", M, N, K);
+    if (K % 8) RV_FAIL("gemm_tcgen05: K = %d must be a multiple of 8 (16-byte rows for TMA)", K);
+    if (((uintptr_t)x | (uintptr_t)w) % 16) RV_FAIL("gemm_tcgen05: operands must be 16-byte aligned");
+    const int n_pad = ((M + 15) / 16) * 16;
+    const int tiles = (N + RV_GEMM_BM - 1) / RV_GEMM_BM;
+    const int kblocks = (K + RV_GEMM_BK - 1) / RV_GEMM_BK;
+    const int splits = rv_gemm_tcgen05_splits(N, K);
+    const int stages = pick_stages(n_pad);
+    const size_t ring = (size_t)stages * (RV_GEMM_BM * RV_GEMM_BK * 2 + n_pad * RV_GEMM_BK * 2);
+    if (stages < 2) RV_FAIL("gemm_tcgen05: no room for two stages with %d tokens", M);
+    if (splits > 1 && (size_t)M * RV_GEMM_BM * 4 > ring)
+        RV_FAIL("gemm_tcgen05: the partial tile of %d tokens does not fit the stage ring", M);
+    CUtensorMap map_w, map_x;
+    if (make_map(&map_w, w, N, K, RV_GEMM_BM)) return 1;
+    if (make_map(&map_x, x, M, K, n_pad)) return 1;
+    const size_t smem = ring + 1024;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (out_dtype == RV_DTYPE_BF16)
+        return launch<bf16>(map_w, map_x, out, status, M, N, kblocks, n_pad, stages, tiles, splits, smem, s);
+    if (out_dtype == RV_DTYPE_F32)
+        return launch<float>(map_w, map_x, out, status, M, N, kblocks, n_pad, stages, tiles, splits, smem, s);
+    RV_FAIL("gemm_tcgen05: unknown output dtype code %d", out_dtype);
+}

@@ -17,6 +17,7 @@ __global__ void qk_norm_rope_write_kernel(
     float eps, const float* __restrict__ cos_table, const float* __restrict__ sin_table,
     const int* __restrict__ positions, const int* __restrict__ slot_mapping,
     T* __restrict__ k_cache, T* __restrict__ v_cache) {
+    rv_pdl_prologue();
     const int heads_total = num_heads + 2 * num_kv_heads;
     const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
@@ -99,7 +100,7 @@ extern "C" int rv_qk_norm_rope_write(void* qkv, int dtype, int row_stride, int n
     const long long blocks = (warps + 3) / 4;
     if (blocks > 0x7fffffffLL) RV_FAIL("qk_norm_rope_write: too many rows");
     RV_DISPATCH_DTYPE(dtype, "qk_norm_rope_write",
-                      (qk_norm_rope_write_kernel<T><<<(int)blocks, 128, 0, (cudaStream_t)stream>>>(
+                      (rv_launch(qk_norm_rope_write_kernel<T>, dim3((int)blocks), dim3(128), 0, (cudaStream_t)stream, 
                           (T*)qkv, row_stride, n_tokens, num_heads, num_kv_heads, head_dim,
                           q_weight, k_weight, eps, cos_table, sin_table, positions, slot_mapping,
                           (T*)k_cache, (T*)v_cache)));

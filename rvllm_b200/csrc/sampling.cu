@@ -15,56 +15,100 @@
 // src/sampler.rs:118-129).  Plain reference: tests/plain_ops.py sample_row.
 #include "common.cuh"
 
-__global__ void argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab) {
-    __shared__ float sv[32];
-    __shared__ int si[32];
-    const float* row = logits + (size_t)blockIdx.x * vocab;
-    float best = -INFINITY;
-    int idx = 0x7fffffff;
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-        const float v = row[i];
-        if (v > best) {   // false for NaN; strict, so the earliest index of a thread stays
-            best = v;
-            idx = i;
-        }
-    }
-    auto better = [](float v, int i, float bv, int bi) { return v > bv || (v == bv && i < bi); };
+// Stage 1: block (row, part) scans its slice of the row; stage 2 combines the parts.
+// A candidate is (value, index); the better one has the larger value, or on a tie the
+// smaller index, so the result does not depend on how the row is cut.
+struct RvBest { float v; int i; };
+__device__ __forceinline__ RvBest rv_better(RvBest a, RvBest b) {
+    return (b.v > a.v || (b.v == a.v && b.i < a.i)) ? b : a;
+}
+__device__ __forceinline__ RvBest rv_block_best(RvBest x, float* sv, int* si) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
-        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-        const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
-        if (better(ov, oi, best, idx)) {
-            best = ov;
-            idx = oi;
-        }
+        RvBest y;
+        y.v = __shfl_xor_sync(0xffffffffu, x.v, o);
+        y.i = __shfl_xor_sync(0xffffffffu, x.i, o);
+        x = rv_better(x, y);
     }
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    if (lane == 0) {
-        sv[warp] = best;
-        si[warp] = idx;
-    }
+    if (lane == 0) { sv[warp] = x.v; si[warp] = x.i; }
     __syncthreads();
     if (warp == 0) {
         const int nw = blockDim.x >> 5;
-        best = lane < nw ? sv[lane] : -INFINITY;
-        idx = lane < nw ? si[lane] : 0x7fffffff;
+        x.v = lane < nw ? sv[lane] : -INFINITY;
+        x.i = lane < nw ? si[lane] : 0x7fffffff;
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
-            if (better(ov, oi, best, idx)) {
-                best = ov;
-                idx = oi;
-            }
+            RvBest y;
+            y.v = __shfl_xor_sync(0xffffffffu, x.v, o);
+            y.i = __shfl_xor_sync(0xffffffffu, x.i, o);
+            x = rv_better(x, y);
         }
-        if (lane == 0) out[blockIdx.x] = idx == 0x7fffffff ? 0 : idx;
+    }
+    return x;   // valid in warp 0
+}
+
+__global__ void argmax_parts_kernel(const float* __restrict__ logits, float* __restrict__ part_v,
+                                    int* __restrict__ part_i, int vocab, int parts) {
+    rv_pdl_prologue();
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    const float* row = logits + (size_t)blockIdx.x * vocab;
+    const int per = (vocab + parts - 1) / parts;
+    const int a = blockIdx.y * per, b = min(vocab, a + per);
+    RvBest best = {-INFINITY, 0x7fffffff};
+    for (int i = a + threadIdx.x; i < b; i += blockDim.x) {
+        const float v = row[i];
+        if (v > best.v) { best.v = v; best.i = i; }   // false for NaN; strict keeps the earliest
+    }
+    best = rv_block_best(best, sv, si);
+    if (threadIdx.x == 0) {
+        part_v[blockIdx.x * parts + blockIdx.y] = best.v;
+        part_i[blockIdx.x * parts + blockIdx.y] = best.i;
     }
 }
 
-extern "C" int rv_argmax(const float* logits, int* out, int n_rows, int vocab, void* stream) {
+__global__ void argmax_final_kernel(const float* __restrict__ part_v, const int* __restrict__ part_i,
+                                    int* __restrict__ out, int parts) {
+    rv_pdl_prologue();
+    RvBest best = {-INFINITY, 0x7fffffff};
+    for (int p = threadIdx.x; p < parts; p += 32) {
+        RvBest c = {part_v[blockIdx.x * parts + p], part_i[blockIdx.x * parts + p]};
+        best = rv_better(best, c);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        RvBest y;
+        y.v = __shfl_xor_sync(0xffffffffu, best.v, o);
+        y.i = __shfl_xor_sync(0xffffffffu, best.i, o);
+        best = rv_better(best, y);
+    }
+    if (threadIdx.x == 0) out[blockIdx.x] = best.i == 0x7fffffff ? 0 : best.i;
+}
+
+#define RV_ARGMAX_MAX_PARTS 64
+
+// `scratch` holds rows * parts (value, index) pairs: rows * parts * 8 bytes, parts as
+// given by rv_argmax_parts.
+extern "C" int rv_argmax_parts(int n_rows, int vocab) {
+    int parts = 1;
+    while (parts < RV_ARGMAX_MAX_PARTS && n_rows * parts < 296 && vocab / (parts * 2) >= 1024) parts *= 2;
+    return parts;
+}
+
+extern "C" int rv_argmax(const float* logits, int* out, void* scratch, long long scratch_bytes,
+                         int n_rows, int vocab, void* stream) {
     if (n_rows == 0) return 0;
     if (n_rows < 0 || vocab <= 0) RV_FAIL("argmax: bad sizes");
-    argmax_kernel<<<n_rows, 1024, 0, (cudaStream_t)stream>>>(logits, out, vocab);
+    if (n_rows > 65535) RV_FAIL("argmax: too many rows for one launch");
+    const int parts = rv_argmax_parts(n_rows, vocab);
+    if ((long long)n_rows * parts * 8 > scratch_bytes) RV_FAIL("argmax: scratch too small");
+    float* part_v = (float*)scratch;
+    int* part_i = (int*)((char*)scratch + (size_t)n_rows * parts * 4);
+    cudaStream_t s = (cudaStream_t)stream;
+    rv_launch(argmax_parts_kernel, dim3(dim3(n_rows, parts)), dim3(256), 0, s, logits, part_v, part_i, vocab, parts);
+    RV_CHECK_LAUNCH("argmax");
+    rv_launch(argmax_final_kernel, dim3(n_rows), dim3(32), 0, s, part_v, part_i, out, parts);
     RV_CHECK_LAUNCH("argmax");
     return 0;
 }
@@ -83,6 +127,7 @@ __global__ void __launch_bounds__(RV_SAMPLE_THREADS) sample_kernel(
     const float* __restrict__ logits, const float* __restrict__ temperature,
     const float* __restrict__ top_p, const long long* __restrict__ seed,
     const long long* __restrict__ counter, int* __restrict__ out, int vocab) {
+    rv_pdl_prologue();
     __shared__ float scratch[33];
     __shared__ float seg_sum[RV_SAMPLE_THREADS];
     __shared__ int chosen_thread;
@@ -169,7 +214,7 @@ extern "C" int rv_sample(const float* logits, const float* temperature, const fl
                          int vocab, void* stream) {
     if (n_rows == 0) return 0;
     if (n_rows < 0 || vocab <= 0) RV_FAIL("sample: bad sizes");
-    sample_kernel<<<n_rows, RV_SAMPLE_THREADS, 0, (cudaStream_t)stream>>>(
+    rv_launch(sample_kernel, dim3(n_rows), dim3(RV_SAMPLE_THREADS), 0, (cudaStream_t)stream, 
         logits, temperature, top_p, seed, counter, out, vocab);
     RV_CHECK_LAUNCH("sample");
     return 0;

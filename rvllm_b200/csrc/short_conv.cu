@@ -32,6 +32,7 @@ __global__ void short_conv_kernel(const T* __restrict__ proj, const float* __res
                                   const int* __restrict__ q_start, const int* __restrict__ state_slot,
                                   const int* __restrict__ start_pos, T* __restrict__ out,
                                   int hidden, int taps) {
+    rv_pdl_prologue();
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= hidden) return;
     const int r = blockIdx.y;
@@ -128,7 +129,7 @@ extern "C" int rv_short_conv(const void* proj, int dtype, const float* filter, c
     if (n_reqs > 65535 || chunks > 65535) RV_FAIL("short_conv: batch too large for one launch");
     dim3 grid((hidden + 127) / 128, n_reqs, chunks);
     RV_DISPATCH_DTYPE(dtype, "short_conv",
-                      (short_conv_kernel<T><<<grid, 128, 0, (cudaStream_t)stream>>>(
+                      (rv_launch(short_conv_kernel<T>, dim3(grid), dim3(128), 0, (cudaStream_t)stream, 
                           (const T*)proj, filter, in_bias, conv_bias, state, q_start, state_slot,
                           start_pos, (T*)out, hidden, taps)));
     RV_CHECK_LAUNCH("short_conv");

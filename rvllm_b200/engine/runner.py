@@ -33,6 +33,7 @@ class ModelRunner:
         self._graphs: Dict[Tuple[int, int], "_DecodeGraph"] = {}
         self.steps = 0
         self.graph_steps = 0
+        self.capture_failures = 0
 
     # ---- requests ----------------------------------------------------------------
 
@@ -144,7 +145,27 @@ class ModelRunner:
         if g is None:
             g = _DecodeGraph(self, bucket, block_bucket)
             self._graphs[key] = g
-        logits = g.run(full, device_tokens)
+        logits = None
+        if not g.broken:
+            try:
+                logits = g.run(full, device_tokens)
+            except RuntimeError as e:
+                if g.graph is not None and not g.capturing:
+                    raise                     # a replay failed: not something to hide
+                # The capture itself failed (a library call that cannot be captured, for
+                # instance).  Nothing has run on real tokens yet, so this step and later ones
+                # of this shape are launched kernel by kernel instead.
+                g.broken = True
+                g.graph = None
+                self.capture_failures += 1
+                import warnings
+                warnings.warn(f"capturing a decode graph for batch {bucket} failed ({e}); "
+                              f"running such steps without a graph")
+        if logits is None:
+            ctx = self.builder.build(ordered)
+            if device_tokens is not None:
+                ctx.token_ids[:r].copy_(device_tokens)
+            return self.model.forward(ctx, self.cache.views())
         self.graph_steps += 1
         rows = [i for i, e in enumerate(ordered) for _ in e.want]
         if rows == list(range(r)):
@@ -167,6 +188,8 @@ class _DecodeGraph:
         self.dev = torch.empty(words, dtype=torch.int32, device=runner.device)
         self.graph = None
         self.logits = None
+        self.broken = False
+        self.capturing = False
 
     def _build(self, entries) -> StepContext:
         ctx = self.runner.builder.build(entries, pad_reqs=self.bucket,
@@ -190,10 +213,20 @@ class _DecodeGraph:
             if device_tokens is not None:
                 ctx.token_ids[:len(entries)].copy_(device_tokens)
             torch.cuda.synchronize()
+            # A matrix-library workspace cached from a capture whose memory pool is gone
+            # would be used again on the capture stream: drop the cached workspaces first.
+            clear = getattr(torch._C, "_cuda_clearCublasWorkspaces", None)
+            if clear is not None:
+                clear()
             launches = model.ops.launches
-            self.graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(self.graph):
-                self.logits = model.forward(ctx, views)
+            graph = torch.cuda.CUDAGraph()
+            self.capturing = True
+            try:
+                with torch.cuda.graph(graph):
+                    self.logits = model.forward(ctx, views)
+            finally:
+                self.capturing = False
+            self.graph = graph
             self.kernels_per_replay = model.ops.launches - launches
         else:
             ctx = self._build(entries)

@@ -46,6 +46,7 @@ class CudaOps:
         except OSError as e:
             raise KernelError(f"cannot load the kernel library {path}: {e}") from None
         self.library_path = path
+        self.launches = 0
         self.lib.rv_last_error.restype = ctypes.c_char_p
         self.lib.rv_paged_attention_decode_scratch_bytes.restype = c_longlong
         self._scratch = {}
@@ -55,6 +56,14 @@ class CudaOps:
         # are multiples of 16 up to 128), "simt" = the float32-arithmetic kernels
         self.prefill_attention = os.environ.get("RVLLM_PREFILL_ATTENTION", "mma")
         self.decode_attention = os.environ.get("RVLLM_DECODE_ATTENTION", "mma")
+        # bfloat16 products with at most `gemm_small_m` tokens go to the tcgen05
+        # weight-streaming kernel (gemm_tcgen05.cu), whose weight copies start before the
+        # previous kernel has finished; larger ones go to cuBLAS.  RVLLM_GEMM=cublas sends
+        # everything to cuBLAS, =auto only the shapes with few output tiles and a long K.
+        self.gemm_small_m = int(os.environ.get("RVLLM_GEMM_SMALL_M", "16"))
+        self.gemm_mode = os.environ.get("RVLLM_GEMM", "tcgen05")
+        self._gemm_state = {}
+        self._check(self.lib.rv_gemm_tcgen05_init(), "gemm_tcgen05 set-up")
         # float32 products must be float32: no TF32, no reduced-precision accumulation
         torch.backends.cuda.matmul.allow_tf32 = False
         torch.backends.cudnn.allow_tf32 = False
@@ -115,6 +124,35 @@ class CudaOps:
 
     # ---- matrix product (library) -------------------------------------------------------
 
+    def _gemm_status(self, device):
+        st = self._gemm_state.get(device)
+        if st is None:
+            st = torch.zeros(1, dtype=torch.int32, device=device)
+            self._gemm_state[device] = st
+        return st
+
+    def linear_tcgen05(self, x, w, out_dtype):
+        """y = x . w^T for bfloat16 x [M <= 256, K] and w [N, K] on the tcgen05 kernel."""
+        self._need(x, "activation rows", torch.bfloat16)
+        self._need(w, "weight matrix", torch.bfloat16)
+        m, k = x.shape
+        n = w.shape[0]
+        y = torch.empty((m, n), dtype=out_dtype, device=x.device)
+        self._check(self.lib.rv_gemm_tcgen05(
+            _ptr(x), _ptr(w), _ptr(y), _code(out_dtype), _ptr(self._gemm_status(x.device)),
+            c_int(m), c_int(n), c_int(k), self._stream()), "gemm_tcgen05")
+        return y
+
+    def check_status(self) -> None:
+        """Raise if a kernel recorded that one of its bounded waits ran out (this
+        synchronises with the device)."""
+        for device, st in self._gemm_state.items():
+            code = int(st.item())
+            if code != 0:
+                st.zero_()
+                raise KernelError(f"gemm_tcgen05 gave up waiting on an mbarrier (code {code}) "
+                                  f"on {device}; its output is not valid")
+
     def linear(self, x, w, bias=None, out_dtype=None):
         out_dtype = out_dtype or x.dtype
         if x.dtype != w.dtype:
@@ -123,7 +161,14 @@ class CudaOps:
             x, w = x.to(wide), w.to(wide)
         if x.shape[0] == 0:
             return torch.empty((0, w.shape[0]), dtype=out_dtype, device=x.device)
-        if out_dtype == x.dtype:
+        if (x.dtype == torch.bfloat16 and 0 < x.shape[0] <= self.gemm_small_m
+                and self.gemm_mode != "cublas"
+                and x.shape[1] % 8 == 0 and x.is_contiguous() and w.is_contiguous()
+                and out_dtype in (torch.bfloat16, torch.float32)
+                and (self.gemm_mode == "tcgen05"
+                     or (w.shape[0] <= 18 * 128 and x.shape[1] >= 4096))):
+            y = self.linear_tcgen05(x, w, out_dtype)
+        elif out_dtype == x.dtype:
             y = torch.mm(x, w.t())
         elif x.dtype == torch.bfloat16 and out_dtype == torch.float32:
             y = torch.mm(x, w.t(), out_dtype=torch.float32)
@@ -311,8 +356,11 @@ class CudaOps:
     def argmax(self, logits):
         self._need(logits, "logits", torch.float32)
         out = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
-        self._check(self.lib.rv_argmax(_ptr(logits), _ptr(out), c_int(logits.shape[0]),
+        scratch = torch.empty(logits.shape[0] * 64 * 2, dtype=torch.int32, device=logits.device)
+        self._check(self.lib.rv_argmax(_ptr(logits), _ptr(out), _ptr(scratch),
+                                       c_longlong(scratch.numel() * 4), c_int(logits.shape[0]),
                                        c_int(logits.shape[1]), self._stream()), "argmax")
+        self.launches += 1
         return out
 
     def sample(self, logits, temperature, top_p, seed, counter):

@@ -303,3 +303,32 @@ def test_sample_frequencies(ops):
     freq = torch.bincount(out.long(), minlength=5).double() / n
     p = torch.softmax(logits[0].double() / 0.7, 0)
     assert (freq - p).abs().max() < 0.03
+
+
+GEMM_SHAPES = [
+    # M, N, K: token counts around the padding steps, widths that are no multiple of the
+    # 128-row tile or the 64-element stage, K split over many blocks and not split at all
+    (1, 128, 64), (3, 200, 72), (8, 2048, 2048), (16, 6144, 2048), (17, 1000, 520),
+    (64, 2048, 8192), (100, 384, 96), (128, 16384, 256), (200, 640, 1096), (256, 130, 2048),
+]
+
+
+@pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_tcgen05(ops, M, N, K, out_dtype):
+    g = torch.Generator().manual_seed(12)
+    x = rnd((M, K), torch.bfloat16, g)
+    w = rnd((N, K), torch.bfloat16, g, 0.05)
+    # one entry of x and w made large: a wrong tile, swizzle or K offset cannot hide
+    x[M // 2, K // 3] = 40.0
+    w[N // 5, K // 3] = 3.0
+    ref = x.double() @ w.double().t()
+    for _ in range(2):                            # twice: the tickets must be back at zero
+        y = ops.linear_tcgen05(x.cuda(), w.cuda(), out_dtype)
+        ops.check_status()
+        err = (y.double().cpu() - ref).abs().max() / ref.abs().max()
+        assert err <= (2e-5 if out_dtype == torch.float32 else 5e-3), float(err)
+    # the same numbers whatever rows share the batch: row 0 alone
+    y1 = ops.linear_tcgen05(x[:1].contiguous().cuda(), w.cuda(), torch.float32)
+    yM = ops.linear_tcgen05(x.cuda(), w.cuda(), torch.float32)
+    assert torch.equal(y1[0], yM[0])
