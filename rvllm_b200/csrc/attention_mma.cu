@@ -69,6 +69,91 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     return *(unsigned*)&v;
 }
 
+// One tile of 64 keys for a warp's 16 packed rows: S = Q K^T, mask, online softmax, O += P V.
+// Rows lane/4 ("a") and lane/4 + 8 ("b") of the warp belong to this thread; a key j counts
+// for row a iff lo_a <= j <= hi_a.
+template <int HD>
+__device__ __forceinline__ void attend_tile(const unsigned (&qf)[HD / 16][4], const bf16* kt,
+                                            const bf16* vt, int tile_key0, int lane, int lo_a,
+                                            int hi_a, int lo_b, int hi_b, float scale_log2,
+                                            float& m_a, float& m_b, float& l_a, float& l_b,
+                                            float (&o)[HD / 8][4]) {
+    constexpr int LD = HD + 8;
+    constexpr int KSTEPS = HD / 16;
+    // S = Q K^T for 16 rows x 64 keys
+    float s[RV_BN / 8][4];
+#pragma unroll
+    for (int i = 0; i < RV_BN / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < KSTEPS; ++kk) {
+#pragma unroll
+        for (int nb = 0; nb < RV_BN / 16; ++nb) {
+            unsigned b[4];
+            ldmatrix_x4(b, kt + (nb * 16 + (lane & 7) + (lane >> 4) * 8) * LD + kk * 16 +
+                               ((lane >> 3) & 1) * 8);
+            mma_bf16(s[2 * nb], qf[kk], b[0], b[1]);
+            mma_bf16(s[2 * nb + 1], qf[kk], b[2], b[3]);
+        }
+    }
+    // mask, scale, running maximum
+    const int key0 = tile_key0 + (lane & 3) * 2;
+    float mx_a = -INFINITY, mx_b = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < RV_BN / 8; ++i) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const int key = key0 + i * 8 + e;
+            s[i][e] = (key >= lo_a && key <= hi_a) ? s[i][e] * scale_log2 : -INFINITY;
+            s[i][2 + e] = (key >= lo_b && key <= hi_b) ? s[i][2 + e] * scale_log2 : -INFINITY;
+            mx_a = fmaxf(mx_a, s[i][e]);
+            mx_b = fmaxf(mx_b, s[i][2 + e]);
+        }
+    }
+    mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
+    mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
+    mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
+    mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+    const float mn_a = fmaxf(m_a, mx_a), mn_b = fmaxf(m_b, mx_b);
+    const float off_a = mn_a == -INFINITY ? 0.f : mn_a, off_b = mn_b == -INFINITY ? 0.f : mn_b;
+    const float corr_a = exp2f(m_a - off_a), corr_b = exp2f(m_b - off_b);   // m = -inf -> 0
+    m_a = mn_a;
+    m_b = mn_b;
+    l_a *= corr_a;
+    l_b *= corr_b;
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) {
+        o[i][0] *= corr_a; o[i][1] *= corr_a;
+        o[i][2] *= corr_b; o[i][3] *= corr_b;
+    }
+    // P = exp2(S - m), rounded to bfloat16 for the second product; the row sum adds the
+    // rounded values, so numerator and denominator see the same numbers
+    unsigned pa[RV_BN / 16][4];
+#pragma unroll
+    for (int i = 0; i < RV_BN / 8; ++i) {
+        const float e0 = exp2f(s[i][0] - off_a), e1 = exp2f(s[i][1] - off_a);
+        const float e2 = exp2f(s[i][2] - off_b), e3 = exp2f(s[i][3] - off_b);
+        const __nv_bfloat162 ra = __floats2bfloat162_rn(e0, e1);
+        const __nv_bfloat162 rb = __floats2bfloat162_rn(e2, e3);
+        const float2 fa = __bfloat1622float2(ra), fb = __bfloat1622float2(rb);
+        l_a += fa.x + fa.y;
+        l_b += fb.x + fb.y;
+        pa[i >> 1][(i & 1) * 2] = *(const unsigned*)&ra;
+        pa[i >> 1][(i & 1) * 2 + 1] = *(const unsigned*)&rb;
+    }
+    // O += P V
+#pragma unroll
+    for (int kk = 0; kk < RV_BN / 16; ++kk) {
+#pragma unroll
+        for (int nd = 0; nd < HD / 16; ++nd) {
+            unsigned b[4];
+            ldmatrix_x4_trans(b, vt + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LD +
+                                     nd * 16 + (lane >> 4) * 8);
+            mma_bf16(o[2 * nd], pa[kk], b[0], b[1]);
+            mma_bf16(o[2 * nd + 1], pa[kk], b[2], b[3]);
+        }
+    }
+}
+
 template <int HD, int NWARPS, bool SPLIT>
 __global__ void __launch_bounds__(NWARPS * 32) paged_attention_mma_kernel(
     const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ k_cache,
@@ -203,78 +288,8 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_attention_mma_kernel(
         const bf16* kt = Ks + stage * RV_BN * LD;
         const bf16* vt = Vs + stage * RV_BN * LD;
 
-        // S = Q K^T for 16 rows x 64 keys
-        float s[RV_BN / 8][4];
-#pragma unroll
-        for (int i = 0; i < RV_BN / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
-#pragma unroll
-        for (int kk = 0; kk < KSTEPS; ++kk) {
-#pragma unroll
-            for (int nb = 0; nb < RV_BN / 16; ++nb) {
-                unsigned b[4];
-                ldmatrix_x4(b, kt + (nb * 16 + (lane & 7) + (lane >> 4) * 8) * LD + kk * 16 +
-                                   ((lane >> 3) & 1) * 8);
-                mma_bf16(s[2 * nb], qf[kk], b[0], b[1]);
-                mma_bf16(s[2 * nb + 1], qf[kk], b[2], b[3]);
-            }
-        }
-        // mask, scale, running maximum
-        const int key0 = t * RV_BN + (lane & 3) * 2;
-        float mx_a = -INFINITY, mx_b = -INFINITY;
-#pragma unroll
-        for (int i = 0; i < RV_BN / 8; ++i) {
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const int key = key0 + i * 8 + e;
-                s[i][e] = (key >= lo_a && key <= hi_a) ? s[i][e] * scale_log2 : -INFINITY;
-                s[i][2 + e] = (key >= lo_b && key <= hi_b) ? s[i][2 + e] * scale_log2 : -INFINITY;
-                mx_a = fmaxf(mx_a, s[i][e]);
-                mx_b = fmaxf(mx_b, s[i][2 + e]);
-            }
-        }
-        mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
-        mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
-        mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
-        mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
-        const float mn_a = fmaxf(m_a, mx_a), mn_b = fmaxf(m_b, mx_b);
-        const float off_a = mn_a == -INFINITY ? 0.f : mn_a, off_b = mn_b == -INFINITY ? 0.f : mn_b;
-        const float corr_a = exp2f(m_a - off_a), corr_b = exp2f(m_b - off_b);   // m = -inf -> 0
-        m_a = mn_a;
-        m_b = mn_b;
-        l_a *= corr_a;
-        l_b *= corr_b;
-#pragma unroll
-        for (int i = 0; i < HD / 8; ++i) {
-            o[i][0] *= corr_a; o[i][1] *= corr_a;
-            o[i][2] *= corr_b; o[i][3] *= corr_b;
-        }
-        // P = exp2(S - m), rounded to bfloat16 for the second product; the row sum adds the
-        // rounded values, so numerator and denominator see the same numbers
-        unsigned pa[RV_BN / 16][4];
-#pragma unroll
-        for (int i = 0; i < RV_BN / 8; ++i) {
-            const float e0 = exp2f(s[i][0] - off_a), e1 = exp2f(s[i][1] - off_a);
-            const float e2 = exp2f(s[i][2] - off_b), e3 = exp2f(s[i][3] - off_b);
-            const __nv_bfloat162 ra = __floats2bfloat162_rn(e0, e1);
-            const __nv_bfloat162 rb = __floats2bfloat162_rn(e2, e3);
-            const float2 fa = __bfloat1622float2(ra), fb = __bfloat1622float2(rb);
-            l_a += fa.x + fa.y;
-            l_b += fb.x + fb.y;
-            pa[i >> 1][(i & 1) * 2] = *(const unsigned*)&ra;
-            pa[i >> 1][(i & 1) * 2 + 1] = *(const unsigned*)&rb;
-        }
-        // O += P V
-#pragma unroll
-        for (int kk = 0; kk < RV_BN / 16; ++kk) {
-#pragma unroll
-            for (int nd = 0; nd < HD / 16; ++nd) {
-                unsigned b[4];
-                ldmatrix_x4_trans(b, vt + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LD +
-                                         nd * 16 + (lane >> 4) * 8);
-                mma_bf16(o[2 * nd], pa[kk], b[0], b[1]);
-                mma_bf16(o[2 * nd + 1], pa[kk], b[2], b[3]);
-            }
-        }
+        attend_tile<HD>(qf, kt, vt, t * RV_BN, lane, lo_a, hi_a, lo_b, hi_b, scale_log2, m_a, m_b, l_a,
+                        l_b, o);
         __syncthreads();    // every warp is done with this stage before it is refilled
     }
     l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
@@ -316,6 +331,138 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_attention_mma_kernel(
             for (int i = 0; i < HD / 8; ++i)
                 *(unsigned*)(dst + i * 8) = pack_bf16(o[i][2] * inv, o[i][3] * inv);
         }
+    }
+}
+
+// Decode: one token per request.  A block owns 16 packed rows (the query heads of one
+// key/value head) and one split of 256 keys; its four warps take one tile of 64 keys each,
+// so all four tiles are in flight at once, and their results are combined in warp order in
+// shared memory before the split's partial result is written.
+template <int HD>
+__global__ void __launch_bounds__(128) paged_attention_decode_mma_kernel(
+    const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ k_cache,
+    const bf16* __restrict__ v_cache, const int* __restrict__ block_table, int max_blocks,
+    const int* __restrict__ ctx_lens, float* __restrict__ part_o, float2* __restrict__ part_ml,
+    int max_splits, int num_heads, int num_kv_heads, int page_size, float scale_log2, int window) {
+    rv_pdl_prologue();
+    constexpr int LD = HD + 8;
+    constexpr int CPR = HD / 8;
+    constexpr int KSTEPS = HD / 16;
+    constexpr int TILE = RV_BN * LD;                   // elements of one K or V tile
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* Qs = (bf16*)smem_raw;                        // [16][LD]
+    bf16* KV = Qs + 16 * LD;                           // [4 warps][K tile, V tile]
+    const int G = num_heads / num_kv_heads;
+    const int r = blockIdx.z;
+    const int clen = ctx_lens[r];
+    if (clen == 0) return;
+    const int tiles_per_head = (G + 15) / 16;
+    const int g = blockIdx.y / tiles_per_head;
+    const int m0 = (blockIdx.y % tiles_per_head) * 16;
+    const int split = blockIdx.x;
+    const int p = clen - 1;
+    const int key_lo = max(window > 0 ? max(0, p - window + 1) : 0, split * RV_SPLIT);
+    const int key_hi = min(p, split * RV_SPLIT + RV_SPLIT - 1);
+    if (key_lo > key_hi) return;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int page_shift = (page_size & (page_size - 1)) == 0 ? 31 - __clz(page_size) : -1;
+    const int* table = block_table + (size_t)r * max_blocks;
+    const size_t kv_row = (size_t)num_kv_heads * HD;
+    const int rows = min(16, G - m0);
+
+    for (int c = tid; c < 16 * CPR; c += 128) {
+        const int m = c / CPR, ch = c - m * CPR;
+        const bool valid = m < rows;
+        const bf16* src = q + (size_t)r * q_stride + (size_t)(g * G + m0 + (valid ? m : 0)) * HD + ch * 8;
+        cp_async_16(Qs + m * LD + ch * 8, src, valid);
+    }
+    const int t = split * (RV_SPLIT / RV_BN) + warp;   // this warp's tile
+    const bool active = t * RV_BN <= key_hi && t * RV_BN + RV_BN - 1 >= key_lo;
+    bf16* kt = KV + warp * 2 * TILE;
+    bf16* vt = kt + TILE;
+    if (active) {
+        constexpr int ROWS = RV_BN * CPR / 32;
+        size_t off[ROWS];
+        bool valid[ROWS];
+#pragma unroll
+        for (int i = 0; i < ROWS; ++i) {
+            const int c = lane + i * 32;
+            const int row = c / CPR;
+            const int j = t * RV_BN + row;
+            int page = -1;
+            if (j < clen) page = table[page_shift >= 0 ? (j >> page_shift) : (j / page_size)];
+            valid[i] = page >= 0;
+            const int in_page = page_shift >= 0 ? (j & (page_size - 1)) : (j % page_size);
+            off[i] = valid[i] ? ((size_t)page * page_size + in_page) * kv_row + (size_t)g * HD +
+                                    (c - row * CPR) * 8 : 0;
+        }
+#pragma unroll
+        for (int i = 0; i < ROWS; ++i) {
+            const int c = lane + i * 32;
+            const int row = c / CPR, ch = c - row * CPR;
+            cp_async_16(kt + row * LD + ch * 8, k_cache + off[i], valid[i]);
+            cp_async_16(vt + row * LD + ch * 8, v_cache + off[i], valid[i]);
+        }
+    }
+    cp_async_commit();
+    cp_async_wait<0>();
+    __syncthreads();
+
+    const int row_a = m0 + (lane >> 2), row_b = row_a + 8;
+    const bool ok_a = row_a < G, ok_b = row_b < G;
+    const int lo_a = key_lo, lo_b = key_lo;
+    const int hi_a = ok_a ? key_hi : -1, hi_b = ok_b ? key_hi : -1;
+    float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
+    float o[HD / 8][4];
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    if (active) {
+        unsigned qf[KSTEPS][4];
+#pragma unroll
+        for (int kk = 0; kk < KSTEPS; ++kk)
+            ldmatrix_x4(qf[kk], Qs + (lane & 15) * LD + kk * 16 + (lane >> 4) * 8);
+        attend_tile<HD>(qf, kt, vt, t * RV_BN, lane, lo_a, hi_a, lo_b, hi_b, scale_log2, m_a, m_b, l_a,
+                        l_b, o);
+    }
+    l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
+    l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+    l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
+    l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+    __syncthreads();                                    // the tiles are no longer needed
+
+    // park every warp's rows: red[warp][row][HD + 2] float32 over the tile memory
+    float* red = (float*)KV;
+    constexpr int RS = HD + 2;
+    const int col = (lane & 3) * 2;
+    {
+        float* mine_a = red + ((size_t)warp * 16 + (lane >> 2)) * RS;
+        float* mine_b = mine_a + 8 * RS;
+#pragma unroll
+        for (int i = 0; i < HD / 8; ++i) {
+            mine_a[i * 8 + col] = o[i][0]; mine_a[i * 8 + col + 1] = o[i][1];
+            mine_b[i * 8 + col] = o[i][2]; mine_b[i * 8 + col + 1] = o[i][3];
+        }
+        if ((lane & 3) == 0) {
+            mine_a[HD] = m_a; mine_a[HD + 1] = l_a;
+            mine_b[HD] = m_b; mine_b[HD + 1] = l_b;
+        }
+    }
+    __syncthreads();
+    const float ln2 = 0.6931471805599453f;
+    for (int i = tid; i < rows * HD; i += 128) {
+        const int m = i / HD, d = i - m * HD;
+        float M = -INFINITY;
+        for (int w = 0; w < 4; ++w) M = fmaxf(M, red[((size_t)w * 16 + m) * RS + HD]);
+        float L = 0.f, O = 0.f;
+        for (int w = 0; w < 4; ++w) {
+            const float* src = red + ((size_t)w * 16 + m) * RS;
+            const float f = src[HD] == -INFINITY ? 0.f : exp2f(src[HD] - M);
+            L += src[HD + 1] * f;
+            O += src[d] * f;
+        }
+        const size_t slot = ((size_t)r * num_heads + g * G + m0 + m) * max_splits + split;
+        part_o[slot * HD + d] = O;
+        if (d == 0) part_ml[slot] = make_float2(M * ln2, L);
     }
 }
 
@@ -389,9 +536,9 @@ extern "C" int RV_SYM(rv_paged_attention_decode_mma)(
     if (n_reqs > 65535 || num_kv_heads * tiles_per_head > 65535)
         return fail("paged_attention_decode_mma: batch too large for one launch");
     static bool configured = false;
-    const size_t smem = smem_bytes<1>();
+    const size_t smem = (size_t)(16 + 8 * RV_BN) * (RV_HD + 8) * sizeof(bf16);
     if (!configured && smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(paged_attention_mma_kernel<RV_HD, 1, true>,
+        cudaError_t e = cudaFuncSetAttribute(paged_attention_decode_mma_kernel<RV_HD>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return fail(cudaGetErrorString(e));
         configured = true;
@@ -399,10 +546,10 @@ extern "C" int RV_SYM(rv_paged_attention_decode_mma)(
     dim3 grid(max_splits, num_kv_heads * tiles_per_head, n_reqs);
     float* part_o = (float*)scratch;
     float2* part_ml = (float2*)((char*)scratch + slots * RV_HD * 4);
-    rv_launch(paged_attention_mma_kernel<RV_HD, 1, true>, dim3(grid), dim3(32), smem, (cudaStream_t)stream, 
-        (const bf16*)q, q_stride, (const bf16*)k_cache, (const bf16*)v_cache, block_table,
-        max_blocks, q_start, ctx_lens, nullptr, part_o, part_ml, max_splits, 0, num_heads,
-        num_kv_heads, page_size, scale * 1.4426950408889634f, window);
+    rv_launch(paged_attention_decode_mma_kernel<RV_HD>, dim3(grid), dim3(128), smem,
+              (cudaStream_t)stream, (const bf16*)q, q_stride, (const bf16*)k_cache,
+              (const bf16*)v_cache, block_table, max_blocks, ctx_lens, part_o, part_ml, max_splits,
+              num_heads, num_kv_heads, page_size, scale * 1.4426950408889634f, window);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fail(cudaGetErrorString(e));
     return 0;
