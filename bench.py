@@ -205,6 +205,9 @@ def run_ours(args):
     step_bytes = weight_bytes + B * mean_ctx * kv_bytes_per_token + B * conv_state_bytes
     achieved = step_bytes / (ms_per_step / 1e3) / 1e9
 
+    if args.only == "breakdown":
+        return run_breakdown(torch, fresh_runner, do_prefill, prompts, B, ops)
+
     if args.only == "decode":
         print(json.dumps({"only": "decode", "value": round(value, 1),
                           "ms_per_step": round(ms_per_step, 4), "gpu_launches": launches,
@@ -304,6 +307,44 @@ def run_prefill_only(torch, fresh_runner, prompts, StepEntry):
     return 0
 
 
+def run_breakdown(torch, fresh_runner, do_prefill, prompts, B, ops, ctx=3000, steps=20):
+    """Per-kernel device time inside replayed decode steps (torch.profiler over `steps`
+    steps at context `ctx`), the wall time of a step, and the host time of an engine step.
+    With programmatic dependent launch a kernel's time includes its wait for the previous
+    kernel, so the kernel times can add up to more than the wall time."""
+    import collections
+    import re
+
+    from torch.profiler import ProfilerActivity, profile
+    runner = fresh_runner(B)
+    do_prefill(runner, prompts(B, ctx))
+    reqs = list(range(B))
+    runner.decode_greedy(reqs, [1] * B, 8)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    runner.decode_greedy(reqs, [1] * B, 50)
+    e1.record()
+    torch.cuda.synchronize()
+    wall_us = e0.elapsed_time(e1) / 50 * 1e3
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        runner.decode_greedy(reqs, [1] * B, steps)
+        torch.cuda.synchronize()
+    agg = collections.defaultdict(lambda: [0, 0.0])
+    for ev in prof.events():
+        if ev.device_type == torch.autograd.DeviceType.CUDA:
+            name = re.sub(r"<.*", "", ev.name).replace("void ", "")[:48]
+            agg[name][0] += 1
+            agg[name][1] += ev.device_time
+    ops.check_status()
+    kernels = {k: {"per_step": round(n / steps, 1), "us_each": round(t / n, 2),
+                   "us_per_step": round(t / steps, 1)}
+               for k, (n, t) in sorted(agg.items(), key=lambda x: -x[1][1])[:16]}
+    print(json.dumps({"only": "breakdown", "batch": B, "context": ctx,
+                      "wall_us_per_step": round(wall_us, 1), "kernels": kernels}))
+    return 0
+
+
 def run_kernels(args):
     """Single kernels at LFM2-1.2B sizes, timed as launches captured in one CUDA graph (no
     host gaps), over operands larger than L2.  One JSON line."""
@@ -378,11 +419,14 @@ def run_kernels(args):
         flops = 4 * nh * hd * T * (T + 1) / 2
         out[f"attn_prefill_t{T}"] = {"us": round(us, 1), "TFLOP/s": round(flops / us / 1e6, 1),
                                      "frac_bf16": round(flops / us / 1e6 / pk["bf16_tflops"], 3)}
-    if args.kernel in ("all", "gemm"):
+    if args.kernel == "all" or args.kernel.startswith("gemm"):
         M = 8
         x = torch.randn(M, 8192, device="cuda", dtype=torch.bfloat16)
-        for N, K in ((6144, 2048), (2048, 2048), (3072, 2048), (16384, 2048), (2048, 8192),
-                     (65536, 2048)):
+        shapes = ((6144, 2048), (2048, 2048), (3072, 2048), (16384, 2048), (2048, 8192),
+                  (65536, 2048))
+        if ":" in args.kernel:                       # gemm:NxK, one shape (for profiling)
+            shapes = (tuple(int(v) for v in args.kernel.split(":")[1].split("x")),)
+        for N, K in shapes:
             copies = max(4, min(48, (300 << 20) // (N * K * 2)))
             ws = [torch.randn(N, K, device="cuda", dtype=torch.bfloat16) for _ in range(copies)]
             xs = x[:, :K].contiguous()
@@ -413,10 +457,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "kernels"],
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "kernels", "breakdown"],
                     help="run one part only (for profiling); the JSON line then lacks the rest")
     ap.add_argument("--kernel", default="all",
-                    help="with --only kernels: attn_decode, attn_prefill, gemm or all")
+                    help="with --only kernels: attn_decode, attn_prefill, gemm, gemm:NxK or all")
     ap.add_argument("--kernel-batch", type=int, default=64)
     ap.add_argument("--kernel-ctx", type=int, default=4096)
     args = ap.parse_args()

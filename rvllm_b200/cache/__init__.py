@@ -1,2 +1,2 @@
-from .manager import CacheManager, CacheView, Group, RequestCache
+from .manager import CacheManager, CacheView, Group, PageTable, RequestCache
 from .pages import PagePool

@@ -24,6 +24,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence
 
+import numpy as np
 import torch
 
 from ..errors import CacheError
@@ -51,12 +52,54 @@ class Group:
     v: Optional[torch.Tensor] = None
 
 
+class PageTable:
+    """A request's page ids in one group, logical page -> physical page (-1 once released).
+    Kept in a numpy array so that a step's batch packing copies it without conversion;
+    indexing and slicing give Python ints and lists."""
+
+    __slots__ = ("_a", "_n")
+
+    def __init__(self):
+        self._a = np.empty(16, dtype=np.int32)
+        self._n = 0
+
+    def append(self, page: int) -> None:
+        if self._n == self._a.shape[0]:
+            grown = np.empty(2 * self._n, dtype=np.int32)
+            grown[:self._n] = self._a
+            self._a = grown
+        self._a[self._n] = page
+        self._n += 1
+
+    def view(self, n: Optional[int] = None) -> np.ndarray:
+        return self._a[:self._n if n is None else n]
+
+    def __len__(self) -> int:
+        return self._n
+
+    def __getitem__(self, i):
+        out = self._a[:self._n][i]
+        return out.tolist() if isinstance(i, slice) else int(out)
+
+    def __setitem__(self, i: int, page: int) -> None:
+        self._a[:self._n][i] = page
+
+    def __iter__(self):
+        return iter(self._a[:self._n].tolist())
+
+    def __eq__(self, other):
+        return list(self) == list(other)
+
+    def __repr__(self):
+        return f"PageTable({list(self)})"
+
+
 @dataclass
 class RequestCache:
     slot: int
     tokens: int = 0                              # positions covered by reserved pages
     computed: int = 0                            # positions whose keys are written
-    tables: List[List[int]] = field(default_factory=list)   # per group, -1 = released
+    tables: List[PageTable] = field(default_factory=list)    # per group, -1 = released
     first_live: List[int] = field(default_factory=list)     # per group: first page kept
 
 
@@ -138,7 +181,7 @@ class CacheManager:
         if req in self.requests:
             raise CacheError(f"request {req!r} is already live")
         rc = RequestCache(slot=self.slots.alloc(),
-                          tables=[[] for _ in self.groups],
+                          tables=[PageTable() for _ in self.groups],
                           first_live=[0 for _ in self.groups])
         self.requests[req] = rc
         return rc
@@ -171,9 +214,12 @@ class CacheManager:
         rc = self.requests[req]
         if total_tokens <= rc.tokens:
             return True
+        want = -(-total_tokens // self.page_size)
+        if all(len(t) >= want for t in rc.tables):
+            rc.tokens = total_tokens                 # room left in the last page
+            return True
         if not self.can_reserve(req, total_tokens):
             return False
-        want = -(-total_tokens // self.page_size)
         for gi, grp in enumerate(self.groups):
             table = rc.tables[gi]
             while len(table) < want:

@@ -30,7 +30,7 @@
 
 #define RV_GEMM_BM 128          // rows of W per block (the MMA's M)
 #define RV_GEMM_BK 64           // K elements per stage: 128 bytes, one swizzle row
-#define RV_GEMM_MAX_STAGES 6
+#define RV_GEMM_MAX_STAGES 12
 #define RV_GEMM_SMEM_LIMIT (226 * 1024)
 #define RV_SPIN_LIMIT (1u << 22)
 
@@ -316,20 +316,51 @@ static int make_map(CUtensorMap* map, const void* ptr, long long rows, long long
     return 0;
 }
 
-// How many blocks share the K range of one tile: a power of two up to 8 (the portable
-// cluster size), enough that about 148 blocks or more stream W, and at least four stages
-// of work each.  Depends on N and K only, so a row's sum order does not depend on M.
+static int env_int(const char* name, int fallback) {
+    const char* e = getenv(name);
+    return e && *e ? atoi(e) : fallback;
+}
+
+// How many blocks (1 to 8, the portable cluster size) share the K range of one tile: doubled
+// until there is about one block per SM, as long as each keeps at least four stages of work.
+// (RVLLM_GEMM_POW2=0 selects a wave-cost model instead; timed on the LFM2-1.2B decode step
+// it was a few per cent slower.)  The split depends on N and K only, so the order of a row's
+// sum does not depend on how many tokens share the launch.
 extern "C" int rv_gemm_tcgen05_splits(int N, int K) {
     const int tiles = (N + RV_GEMM_BM - 1) / RV_GEMM_BM;
     const int kblocks = (K + RV_GEMM_BK - 1) / RV_GEMM_BK;
-    int s = 1;
-    while (s < 8 && tiles * s < 148 && kblocks / (2 * s) >= 4) s *= 2;
-    return s;
+    static int forced = env_int("RVLLM_GEMM_SPLITS", 0);
+    static int fixed_cost = env_int("RVLLM_GEMM_FIXED", 6);
+    static int sms = env_int("RVLLM_GEMM_SLOTS", 444);
+    if (forced > 0) return forced > 8 ? 8 : (kblocks / forced < 1 ? 1 : forced);
+    static int pow2 = env_int("RVLLM_GEMM_POW2", 1);
+    if (pow2) {        // doubling until about one block per SM, at least four stages each
+        int s = 1;
+        while (s < 8 && tiles * s < 148 && kblocks / (2 * s) >= 4) s *= 2;
+        return s;
+    }
+    int best = 1;
+    long long best_cost = -1;
+    for (int s = 1; s <= 8; ++s) {
+        if (s > 1 && kblocks / s < 2) break;
+        const long long waves = ((long long)tiles * s + sms - 1) / sms;
+        const long long cost = waves * ((kblocks + s - 1) / s + fixed_cost);
+        if (best_cost < 0 || cost < best_cost) {
+            best_cost = cost;
+            best = s;
+        }
+    }
+    return best;
 }
 
+// Stages of the copy ring.  Six by default (108 KB with 16 tokens): two blocks fit an SM, so
+// the next kernel's blocks can already fill their rings while this one computes; deeper
+// rings that leave room for one block per SM measured much slower.
 static int pick_stages(int n_pad) {
+    static int want = env_int("RVLLM_GEMM_STAGES", 6);
     const int per_stage = RV_GEMM_BM * RV_GEMM_BK * 2 + n_pad * RV_GEMM_BK * 2;
     int st = (RV_GEMM_SMEM_LIMIT - 1024) / per_stage;
+    if (st > want) st = want;
     return st > RV_GEMM_MAX_STAGES ? RV_GEMM_MAX_STAGES : st;
 }
 

@@ -160,11 +160,16 @@ class BatchBuilder:
         treq = view("token_req")
         tok[n_real:] = 0
         pos[n_real:] = 0
-        for i, (e, s, q) in enumerate(zip(entries, starts, q_lens)):
-            a = int(q_start[i])
-            tok[a:a + q] = np.asarray(e.tokens, dtype=np.int64)
-            pos[a:a + q] = np.arange(s, s + q)
-            treq[a:a + q] = i
+        if n_decode == r_real:                       # single tokens only: no per-request numpy
+            tok[:r_real] = [e.tokens[0] for e in entries]
+            pos[:r_real] = starts
+            treq[:r_real] = range(r_real)
+        else:
+            for i, (e, s, q) in enumerate(zip(entries, starts, q_lens)):
+                a = int(q_start[i])
+                tok[a:a + q] = np.asarray(e.tokens, dtype=np.int64)
+                pos[a:a + q] = np.arange(s, s + q)
+                treq[a:a + q] = i
         if pad:
             treq[n_real:] = np.arange(r_real, R)
         cl = view("ctx_lens"); cl[:r_real] = ctx; cl[r_real:] = 0
@@ -188,14 +193,20 @@ class BatchBuilder:
             slots = view(f"slot{gi}")
             slots[n_real:] = -1
             for i, (rc, s, q) in enumerate(zip(rcs, starts, q_lens)):
-                t = rc.tables[gi]
+                t = rc.tables[gi].view()
                 nb = -(-ctx[i] // ps)
                 table[i, :nb] = t[:nb]
+                a = int(q_start[i])
+                if q == 1:
+                    page = int(t[s // ps])
+                    if page < 0:
+                        raise CacheError("a token would be written to a released page")
+                    slots[a] = page * ps + s % ps
+                    continue
                 p = np.arange(s, s + q)
-                pages = np.asarray(t, dtype=np.int64)[p // ps]
+                pages = t[p // ps].astype(np.int64)
                 if (pages < 0).any():
                     raise CacheError("a token would be written to a released page")
-                a = int(q_start[i])
                 slots[a:a + q] = pages * ps + p % ps
         dev[:cur].copy_(host[:cur], non_blocking=True)
         self.last_h2d_bytes = cur * 4

@@ -53,20 +53,21 @@ class ModelRunner:
         if not entries:
             return torch.empty((0, self.model.spec.vocab_size), dtype=torch.float32,
                                device=self.device)
-        seen = set()
+        requests, limit = self.cache.requests, self.model.spec.max_position
+        if len({e.req for e in entries}) != len(entries):
+            raise ValueError("a request appears twice in one step")
+        totals = []
         for e in entries:
-            if e.req in seen:
-                raise ValueError(f"request {e.req!r} appears twice in one step")
-            seen.add(e.req)
-            if not self.cache.has(e.req):
+            rc = requests.get(e.req)
+            if rc is None:
                 raise CacheError(f"request {e.req!r} is not live")
-            total = self.cache.requests[e.req].computed + len(e.tokens)
-            if total > self.model.spec.max_position:
+            total = rc.computed + len(e.tokens)
+            if total > limit:
                 raise ValueError(f"request {e.req!r}: {total} tokens exceed the model's "
-                                 f"{self.model.spec.max_position} positions")
-        for e in entries:
-            total = self.cache.requests[e.req].computed + len(e.tokens)
-            if not self.cache.reserve(e.req, total):
+                                 f"{limit} positions")
+            totals.append(total)
+        for e, total in zip(entries, totals):
+            if total > requests[e.req].tokens and not self.cache.reserve(e.req, total):
                 raise CacheError(f"out of pages: request {e.req!r} needs room for "
                                  f"{total} tokens")
         # single tokens first; logits keep the callers' order through logit_rows
@@ -88,9 +89,8 @@ class ModelRunner:
                 logits = logits[torch.tensor(perm, device=logits.device, dtype=torch.long)]
         else:
             logits = self._run(ordered)
-        for e in entries:
-            rc = self.cache.requests[e.req]
-            self.cache.advance(e.req, rc.computed + len(e.tokens))
+        for e, total in zip(entries, totals):
+            self.cache.advance(e.req, total)
         self.steps += 1
         return logits
 

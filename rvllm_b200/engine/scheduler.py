@@ -186,7 +186,9 @@ class Scheduler:
                 continue
             if budget < 1:
                 break
-            while not self.cache.can_reserve(seq.request.id, seq.computed + 1):
+            rc = self.cache.requests[seq.request.id]
+            while rc.tokens <= seq.computed and \
+                    not self.cache.can_reserve(seq.request.id, seq.computed + 1):
                 victim = self.running[-1]
                 if victim is seq and len(self.running) == 1:
                     raise RequestError("a lone sequence cannot get a page: the pool is too "
