@@ -32,6 +32,7 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC",
               "--expt-relaxed-constexpr", "--expt-extended-lambda"]
 
 _lock = threading.Lock()
+_variant_locks = {}
 
 
 # Sources compiled on demand with a size baked in, each into a library of its own.
@@ -63,13 +64,23 @@ def source_hash() -> str:
     return h.hexdigest()[:16]
 
 
+_build_dir = None
+
+
 def build_dir() -> str:
     """The in-tree `_build` folder, or a per-user temporary one when that cannot be
     written (a read-only checkout, another user's files)."""
+    global _build_dir
+    if _build_dir is None:
+        _build_dir = _find_build_dir()
+    return _build_dir
+
+
+def _find_build_dir() -> str:
     in_tree = os.path.join(CSRC, "_build")
     try:
         os.makedirs(in_tree, exist_ok=True)
-        probe = os.path.join(in_tree, f".write_{os.getpid()}")
+        probe = os.path.join(in_tree, f".write_{os.getpid()}_{threading.get_ident()}")
         with open(probe, "w"):
             pass
         os.remove(probe)
@@ -143,6 +154,8 @@ def build_variant(source: str, defines: dict, tag: str, verbose: bool = True) ->
     """Compile one of `VARIANT_SOURCES` with the given -D definitions into its own
     library `librvllm_b200_<tag>_<hash>.so`; returns its path."""
     with _lock:
+        lock = _variant_locks.setdefault(tag, threading.Lock())
+    with lock:
         h = hashlib.sha256()
         for name in (source, "common.cuh"):
             with open(os.path.join(CSRC, name), "rb") as f:
