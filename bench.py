@@ -218,7 +218,7 @@ def run_ours(args):
     runner = fresh_runner(B)
     sched = SchedulerConfig(block_size=PAGE, num_blocks=B * (CONTEXT // PAGE),
                             max_num_batched_tokens=8192, prefill_chunk=2048)
-    engine = Engine(runner, sched, CONTEXT)
+    engine = Engine(runner, sched, CONTEXT, lookahead=True)
     e2e_steps = min(K, 512)
     budget = e2e_steps + W + 16          # requests start decoding a few steps apart
     for i, ids in enumerate(prompts(B, CONTEXT - budget)):

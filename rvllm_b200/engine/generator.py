@@ -63,6 +63,8 @@ class Generator:
         self._runner = None
         self._runner_key = None
         self.last_result: Optional[RunResult] = None
+        # launch the next decode step before reading the current one's tokens
+        self.lookahead = os.environ.get("RVLLM_LOOKAHEAD", "1") != "0"
 
     @classmethod
     def load(cls, model_dir: str, tokenizer: Optional[str] = None, device: str = "cuda",
@@ -148,5 +150,5 @@ class Generator:
             requests.append(Request(i, list(p), opts.max_tokens, stops,
                                     SamplingParams(opts.temperature, opts.top_p, opts.seed + i),
                                     arrival))
-        self.last_result = run(runner, requests, cfg, context)
+        self.last_result = run(runner, requests, cfg, context, lookahead=self.lookahead)
         return self.last_result

@@ -48,8 +48,10 @@ class ModelRunner:
 
     # ---- the step ----------------------------------------------------------------
 
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
-        """float32 logits [wanted, vocab], in the order of the entries and of `want`."""
+    def step(self, entries: Sequence[StepEntry], device_tokens=None) -> torch.Tensor:
+        """float32 logits [wanted, vocab], in the order of the entries and of `want`.
+        With `device_tokens` (int32 device tensor, one id per entry) every entry brings one
+        token whose id is taken from that tensor instead of `entry.tokens`."""
         if not entries:
             return torch.empty((0, self.model.spec.vocab_size), dtype=torch.float32,
                                device=self.device)
@@ -73,7 +75,11 @@ class ModelRunner:
         # single tokens first; logits keep the callers' order through logit_rows
         order = sorted(range(len(entries)), key=lambda i: len(entries[i].tokens) != 1)
         ordered = [entries[i] for i in order]
-        if order != list(range(len(entries))):
+        if device_tokens is not None:
+            if any(len(e.tokens) != 1 for e in entries):
+                raise ValueError("device-fed tokens are for single-token entries only")
+            logits = self._run(ordered, device_tokens)
+        elif order != list(range(len(entries))):
             logits = self._run(ordered)
             # rows come out in `ordered` order; put them back in the callers' order
             counts = [len(e.want) for e in ordered]

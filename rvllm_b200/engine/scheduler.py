@@ -266,6 +266,9 @@ class Scheduler:
         total = 0
         for e in plan:
             seq = e.seq
+            if self.seqs.get(seq.request.id) is not seq:      # aborted while the step ran
+                k += int(e.samples)
+                continue
             seq.computed = e.start + e.count
             total += e.count
             if e.count == 1 and e.start >= seq.prompt_len:

@@ -25,12 +25,17 @@ class BatchSampler:
         request has drawn before."""
         if logits.shape[0] == 0:
             return []
+        return self.sample_device(logits, params, counters).tolist()
+
+    def sample_device(self, logits: torch.Tensor, params: Sequence[SamplingParams],
+                      counters: Sequence[int]) -> torch.Tensor:
+        """The same, leaving the ids on the device (int32 [rows]); nothing waits for the GPU."""
         if all(p.is_greedy for p in params):
-            return self.ops.argmax(logits).tolist()
+            return self.ops.argmax(logits)
         dev = logits.device
         temperature = torch.tensor([p.temperature for p in params], dtype=torch.float32, device=dev)
         top_p = torch.tensor([p.top_p for p in params], dtype=torch.float32, device=dev)
         seed = torch.tensor([p.seed & 0x7FFFFFFFFFFFFFFF for p in params], dtype=torch.int64,
                             device=dev)
         counter = torch.tensor(list(counters), dtype=torch.int64, device=dev)
-        return self.ops.sample(logits, temperature, top_p, seed, counter).tolist()
+        return self.ops.sample(logits, temperature, top_p, seed, counter)

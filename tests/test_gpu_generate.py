@@ -128,3 +128,23 @@ def test_trace_run_program(folders, tmp_path):
                     k += 1
                 pos[e["id"]] += len(e["tokens"])
             assert k == arr.shape[0]
+
+
+def test_lookahead_gives_the_same_tokens(folders):
+    """Launching the next decode step before the current one's tokens are read changes
+    nothing a request sees: stop tokens in the middle, requests of different lengths,
+    a pool that forces preemption, and seeded sampling."""
+    from rvllm_b200 import GenerateOptions, Generator
+    rng = random.Random(6)
+    prompts = [[rng.randrange(512) for _ in range(n)] for n in (3, 20, 9, 33)]
+    gen = Generator.load(folders["A"], dtype="float32")
+    cases = [GenerateOptions(max_tokens=30, block_size=8, stop_tokens=[]),
+             GenerateOptions(max_tokens=30, block_size=8, stop_tokens=[97, 5, 300]),
+             GenerateOptions(max_tokens=25, block_size=8, stop_tokens=[], num_blocks=14),
+             GenerateOptions(max_tokens=30, block_size=8, temperature=0.9, top_p=0.8, seed=3)]
+    for opts in cases:
+        gen.lookahead = False
+        want = gen.complete_batch(prompts, opts, arrival_steps=[0, 0, 3, 4])
+        gen.lookahead = True
+        got = gen.complete_batch(prompts, opts, arrival_steps=[0, 0, 3, 4])
+        assert got == want
