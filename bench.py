@@ -43,6 +43,12 @@ LFM2_1_2B = {
     "max_position_embeddings": 4096, "norm_eps": 1e-5, "tie_embedding": True,
     "torch_dtype": "bfloat16", "bos_token_id": 1, "eos_token_id": 7,
 }
+# The other published sizes differ in these keys only.
+SIZES = {
+    "1.2b": {},
+    "700m": {"hidden_size": 1536, "num_attention_heads": 24, "block_ff_dim": 10240},
+    "350m": {"hidden_size": 1024, "num_attention_heads": 16, "block_ff_dim": 6656},
+}
 CONTEXT = 4096
 PREFILL_TOKENS = 2048
 PAGE = 16
@@ -139,6 +145,7 @@ def run_ours(args):
     pk = peaks()
     layers_full = LFM2_1_2B["num_hidden_layers"]
     data = dict(LFM2_1_2B)
+    data.update(SIZES[args.size])
     cfg = config_from_dict(data)
     K, W, B = args.steps, args.warmup, args.batch
     if K + W > CONTEXT - 64:
@@ -266,12 +273,12 @@ def run_ours(args):
         points[f"decode_b{b}"] = round(v, 1)
 
     line = {
-        "metric": "decode tok/s at batch 8 (LFM2-1.2B sizes, context to 4,096)",
+        "metric": f"decode tok/s at batch {B} (LFM2-{args.size.upper()} sizes, context to 4,096)",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
         "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic: random weights (seed 0), "
         "uniform random token ids", "impl": "ours",
-        "config": {"model": "LFM2-1.2B sizes", "layers": cfg.num_hidden_layers,
+        "config": {"model": f"LFM2-{args.size.upper()} sizes", "layers": cfg.num_hidden_layers,
                    "layers_full": layers_full, "hidden": cfg.hidden_size,
                    "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
                    "head_dim": cfg.head_dim, "ffn": cfg.ffn_dim, "vocab": cfg.vocab_size,
@@ -457,6 +464,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--size", default="1.2b", choices=sorted(SIZES),
+                    help="layer sizes: LFM2-1.2B (the default and the headline), 700M or 350M")
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "kernels", "breakdown"],
                     help="run one part only (for profiling); the JSON line then lacks the rest")
     ap.add_argument("--kernel", default="all",
