@@ -116,6 +116,126 @@ __global__ void short_conv_kernel(const T* __restrict__ proj, const float* __res
     }
 }
 
+// The same for filters of at most 4 taps and widths that are a multiple of 4: a thread owns
+// four adjacent channels and moves them with one 8-byte (bfloat16) or 16-byte (float32)
+// access per row, which is what makes long prompt portions run at memory speed.
+__device__ __forceinline__ float4 rv_conv_load4(const float* p) { return *(const float4*)p; }
+__device__ __forceinline__ float4 rv_conv_load4(const __nv_bfloat16* p) {
+    const uint2 raw = *(const uint2*)p;
+    const float2 a = __bfloat1622float2(*(const __nv_bfloat162*)&raw.x);
+    const float2 b = __bfloat1622float2(*(const __nv_bfloat162*)&raw.y);
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void rv_conv_store4(float* p, float4 v) { *(float4*)p = v; }
+__device__ __forceinline__ void rv_conv_store4(__nv_bfloat16* p, float4 v) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 raw;
+    raw.x = *(const unsigned*)&a;
+    raw.y = *(const unsigned*)&b;
+    *(uint2*)p = raw;
+}
+__device__ __forceinline__ float4 rv_f4_add(float4 a, float4 b) {
+    return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w);
+}
+__device__ __forceinline__ float4 rv_f4_mul(float4 a, float4 b) {
+    return make_float4(a.x * b.x, a.y * b.y, a.z * b.z, a.w * b.w);
+}
+
+#define RV_CONV_VEC_TAPS 4
+
+template <typename T>
+__global__ void short_conv_vec4_kernel(const T* __restrict__ proj, const float* __restrict__ filter,
+                                       const float* __restrict__ in_bias,
+                                       const float* __restrict__ conv_bias, float* __restrict__ state,
+                                       const int* __restrict__ q_start,
+                                       const int* __restrict__ state_slot,
+                                       const int* __restrict__ start_pos, T* __restrict__ out,
+                                       int hidden, int taps) {
+    rv_pdl_prologue();
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (c >= hidden) return;
+    const int r = blockIdx.y;
+    const int q0 = q_start[r];
+    const int qlen = q_start[r + 1] - q0;
+    const int t0 = blockIdx.z * RV_CONV_CHUNK;
+    if (t0 >= qlen) return;
+    const int slot = state_slot[r];
+    const int hist = taps - 1;
+    const bool has_state = slot >= 0 && start_pos[r] > 0 && hist > 0;
+    float* st = slot >= 0 ? state + (size_t)slot * hist * hidden + c : nullptr;
+    const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+
+    float4 f[RV_CONV_VEC_TAPS];                        // f[k] = tap k of the four channels
+#pragma unroll
+    for (int k = 0; k < RV_CONV_VEC_TAPS; ++k)
+        f[k] = k < taps ? make_float4(filter[(size_t)c * taps + k], filter[(size_t)(c + 1) * taps + k],
+                                      filter[(size_t)(c + 2) * taps + k],
+                                      filter[(size_t)(c + 3) * taps + k]) : zero;
+    const float4 bb = in_bias ? *(const float4*)(in_bias + c) : zero;
+    const float4 bc = in_bias ? *(const float4*)(in_bias + hidden + c) : zero;
+    const float4 bxb = in_bias ? *(const float4*)(in_bias + 2 * hidden + c) : zero;
+    const float4 cb = conv_bias ? *(const float4*)(conv_bias + c) : zero;
+    const size_t stride = (size_t)3 * hidden;
+
+    auto bx_at = [&](int rel) -> float4 {
+        const T* p = proj + (size_t)(q0 + rel) * stride + c;
+        return rv_f4_mul(rv_f4_add(rv_conv_load4(p), bb), rv_f4_add(rv_conv_load4(p + 2 * hidden), bxb));
+    };
+    float4 old[RV_CONV_VEC_TAPS - 1], win[RV_CONV_VEC_TAPS - 1];
+#pragma unroll
+    for (int i = 0; i < RV_CONV_VEC_TAPS - 1; ++i) {
+        old[i] = zero;
+        win[i] = zero;
+        if (i < hist) {
+            const int rel = t0 - hist + i;
+            if (rel >= 0) {
+                win[i] = bx_at(rel);
+            } else if (has_state) {
+                old[i] = *(const float4*)(st + (size_t)(hist + rel) * hidden);
+                win[i] = old[i];
+            }
+        }
+    }
+    const int t1 = min(t0 + RV_CONV_CHUNK, qlen);
+    for (int t = t0; t < t1; ++t) {
+        const T* p = proj + (size_t)(q0 + t) * stride + c;
+        const float4 bx = rv_f4_mul(rv_f4_add(rv_conv_load4(p), bb),
+                                    rv_f4_add(rv_conv_load4(p + 2 * hidden), bxb));
+        const float4 gate_c = rv_f4_add(rv_conv_load4(p + hidden), bc);
+        float4 acc = zero;
+#pragma unroll
+        for (int k = 0; k < RV_CONV_VEC_TAPS - 1; ++k)
+            if (k < hist) acc = rv_f4_add(acc, rv_f4_mul(f[k], win[k]));
+#pragma unroll
+        for (int k = 0; k < RV_CONV_VEC_TAPS; ++k)
+            if (k == hist) acc = rv_f4_add(acc, rv_f4_mul(f[k], bx));
+        rv_conv_store4(out + (size_t)(q0 + t) * hidden + c, rv_f4_mul(gate_c, rv_f4_add(acc, cb)));
+#pragma unroll
+        for (int k = 0; k < RV_CONV_VEC_TAPS - 2; ++k)
+            if (k + 1 < hist) win[k] = win[k + 1];
+#pragma unroll
+        for (int k = 0; k < RV_CONV_VEC_TAPS - 1; ++k)
+            if (k == hist - 1) win[k] = bx;
+    }
+    if (t0 == 0 && st && hist > 0) {
+#pragma unroll
+        for (int i = 0; i < RV_CONV_VEC_TAPS - 1; ++i) {
+            if (i < hist) {
+                const int w = qlen + i;
+                float4 v = zero;
+                if (w >= hist) {
+                    v = bx_at(w - hist);
+                } else {
+#pragma unroll
+                    for (int k = 0; k < RV_CONV_VEC_TAPS - 1; ++k)
+                        if (k == w) v = old[k];
+                }
+                *(float4*)(st + (size_t)i * hidden) = v;
+            }
+        }
+    }
+}
+
 extern "C" int rv_short_conv(const void* proj, int dtype, const float* filter, const float* in_bias,
                              const float* conv_bias, float* state, const int* q_start,
                              const int* state_slot, const int* start_pos, void* out, int n_reqs,
@@ -127,6 +247,19 @@ extern "C" int rv_short_conv(const void* proj, int dtype, const float* filter, c
     if (taps > 1 && !state) RV_FAIL("short_conv: a filter of length %d needs a state", taps);
     const int chunks = (max_q_len + RV_CONV_CHUNK - 1) / RV_CONV_CHUNK;
     if (n_reqs > 65535 || chunks > 65535) RV_FAIL("short_conv: batch too large for one launch");
+    const bool aligned = ((uintptr_t)proj % 16 == 0) && ((uintptr_t)out % 16 == 0) &&
+                         (!state || (uintptr_t)state % 16 == 0) &&
+                         (!in_bias || (uintptr_t)in_bias % 16 == 0) &&
+                         (!conv_bias || (uintptr_t)conv_bias % 16 == 0);
+    if (taps <= RV_CONV_VEC_TAPS && hidden % 4 == 0 && aligned) {
+        dim3 vgrid((hidden / 4 + 127) / 128, n_reqs, chunks);
+        RV_DISPATCH_DTYPE(dtype, "short_conv",
+                          (rv_launch(short_conv_vec4_kernel<T>, dim3(vgrid), dim3(128), 0,
+                                     (cudaStream_t)stream, (const T*)proj, filter, in_bias, conv_bias,
+                                     state, q_start, state_slot, start_pos, (T*)out, hidden, taps)));
+        RV_CHECK_LAUNCH("short_conv");
+        return 0;
+    }
     dim3 grid((hidden + 127) / 128, n_reqs, chunks);
     RV_DISPATCH_DTYPE(dtype, "short_conv",
                       (rv_launch(short_conv_kernel<T>, dim3(grid), dim3(128), 0, (cudaStream_t)stream, 
