@@ -15,6 +15,9 @@ from __future__ import annotations
 
 from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
+import gc
+import weakref
+
 import torch
 
 from ..errors import CacheError
@@ -31,6 +34,9 @@ class ModelRunner:
         self.builder = BatchBuilder(cache, ops, self.device, pinned=self.is_cuda)
         self.use_graphs = use_graphs and self.is_cuda
         self._graphs: Dict[Tuple[int, int], "_DecodeGraph"] = {}
+        self._shape_graphs: Dict[tuple, "_ShapeGraph"] = {}
+        self._seen_shapes = set()
+        self.max_shape_graphs = 16
         self.steps = 0
         self.graph_steps = 0
         self.capture_failures = 0
@@ -103,10 +109,53 @@ class ModelRunner:
     def _run(self, ordered: List[StepEntry], device_tokens=None) -> torch.Tensor:
         if self.use_graphs and all(len(e.tokens) == 1 for e in ordered):
             return self._run_graph(ordered, device_tokens)
+        if self.use_graphs and device_tokens is None:
+            logits = self._run_repeated_shape(ordered)
+            if logits is not None:
+                return logits
         ctx = self.builder.build(ordered)
         if device_tokens is not None:
             ctx.token_ids[:len(ordered)].copy_(device_tokens)
         return self.model.forward(ctx, self.cache.views())
+
+    def _run_repeated_shape(self, ordered: List[StepEntry]) -> Optional[torch.Tensor]:
+        """Steps with prompt portions: the second time the same shape comes (the same token
+        counts, wanted places and block-table width, as with a fixed portion size), its launch
+        sequence is captured, and from then on replayed.  Returns None when this step has to
+        be launched kernel by kernel."""
+        ps = self.cache.page_size
+        ctx_max = max(self.cache.requests[e.req].computed + len(e.tokens) for e in ordered)
+        blocks = -(-ctx_max // ps)
+        block_bucket = max(16, 1 << (blocks - 1).bit_length())
+        key = (tuple(len(e.tokens) for e in ordered), tuple(tuple(e.want) for e in ordered),
+               block_bucket)
+        g = self._shape_graphs.get(key)
+        if g is None:
+            if key not in self._seen_shapes:
+                if len(self._seen_shapes) > 4096:
+                    self._seen_shapes.clear()
+                self._seen_shapes.add(key)
+                return None
+            if len(self._shape_graphs) >= self.max_shape_graphs:
+                return None
+            g = _ShapeGraph(self, key, block_bucket)
+            self._shape_graphs[key] = g
+        if g.broken:
+            return None
+        try:
+            logits = g.run(ordered)
+        except RuntimeError as e:
+            if g.graph is not None and not g.capturing:
+                raise
+            g.broken = True
+            g.graph = None
+            self.capture_failures += 1
+            import warnings
+            warnings.warn(f"capturing a graph for a step of {sum(key[0])} tokens failed ({e}); "
+                          f"running such steps without a graph")
+            return None
+        self.graph_steps += 1
+        return logits
 
     def decode_greedy(self, reqs: Sequence[Hashable], first_tokens: Sequence[int],
                       steps: int) -> torch.Tensor:
@@ -179,13 +228,35 @@ class ModelRunner:
         return logits[torch.tensor(rows, device=logits.device, dtype=torch.long)]
 
 
+def _capture(graph, fn):
+    """Capture `fn` into `graph`.  Python's cyclic garbage collector must not run meanwhile:
+    if it destroyed an older graph or freed device memory during the capture, the capture
+    would be invalidated (and a graph destroyed from a destructor aborts the process), so
+    garbage is collected before and collection is off during the capture."""
+    torch.cuda.synchronize()
+    gc.collect()
+    # A matrix-library workspace cached from a capture whose memory pool is gone would be
+    # used again on the capture stream: drop the cached workspaces first.
+    clear = getattr(torch._C, "_cuda_clearCublasWorkspaces", None)
+    if clear is not None:
+        clear()
+    was_enabled = gc.isenabled()
+    gc.disable()
+    try:
+        with torch.cuda.graph(graph):
+            return fn()
+    finally:
+        if was_enabled:
+            gc.enable()
+
+
 class _DecodeGraph:
     """A captured launch sequence for `bucket` single-token requests whose block tables
     are `block_bucket` wide.  Its index arrays live at fixed addresses; a step refills
     them and replays."""
 
     def __init__(self, runner: ModelRunner, bucket: int, block_bucket: int):
-        self.runner = runner
+        self.runner = weakref.proxy(runner)     # no cycle: graphs die with their runner
         self.bucket = bucket
         self.block_bucket = block_bucket
         n_groups = len(runner.cache.groups)
@@ -218,18 +289,11 @@ class _DecodeGraph:
             ctx = self._build(entries)
             if device_tokens is not None:
                 ctx.token_ids[:len(entries)].copy_(device_tokens)
-            torch.cuda.synchronize()
-            # A matrix-library workspace cached from a capture whose memory pool is gone
-            # would be used again on the capture stream: drop the cached workspaces first.
-            clear = getattr(torch._C, "_cuda_clearCublasWorkspaces", None)
-            if clear is not None:
-                clear()
             launches = model.ops.launches
             graph = torch.cuda.CUDAGraph()
             self.capturing = True
             try:
-                with torch.cuda.graph(graph):
-                    self.logits = model.forward(ctx, views)
+                self.logits = _capture(graph, lambda: model.forward(ctx, views))
             finally:
                 self.capturing = False
             self.graph = graph
@@ -240,4 +304,47 @@ class _DecodeGraph:
                 ctx.token_ids[:len(entries)].copy_(device_tokens)
         self.graph.replay()
         model.ops.launches += self.kernels_per_replay
+        return self.logits
+
+
+class _ShapeGraph:
+    """A captured launch sequence for one exact step shape (token counts, wanted places,
+    block-table width).  It is captured when the shape comes for the second time, so the
+    libraries have already run these sizes once outside a capture and no warm-up run is
+    needed (a warm-up on real tokens would apply the cache updates twice)."""
+
+    def __init__(self, runner: ModelRunner, key, block_bucket: int):
+        self.runner = weakref.proxy(runner)     # no cycle: graphs die with their runner
+        self.block_bucket = block_bucket
+        n_tokens, n_reqs = sum(key[0]), len(key[0])
+        n_want = sum(len(w) for w in key[1])
+        n_groups = len(runner.cache.groups)
+        words = 4 * n_tokens + 8 * n_reqs + n_want + 64 + \
+            n_groups * (n_tokens + n_reqs * block_bucket + 8)
+        self.host = torch.empty(words, dtype=torch.int32, pin_memory=True)
+        self.dev = torch.empty(words, dtype=torch.int32, device=runner.device)
+        self.graph = None
+        self.logits = None
+        self.broken = False
+        self.capturing = False
+        self.kernels_per_replay = 0
+
+    def run(self, entries) -> torch.Tensor:
+        runner = self.runner
+        ctx = runner.builder.build(entries, pad_blocks=self.block_bucket,
+                                   buffers=(self.host, self.dev))
+        ctx.max_ctx_len = self.block_bucket * runner.cache.page_size
+        if self.graph is None:
+            launches = runner.model.ops.launches
+            graph = torch.cuda.CUDAGraph()
+            self.capturing = True
+            try:
+                self.logits = _capture(
+                    graph, lambda: runner.model.forward(ctx, runner.cache.views()))
+            finally:
+                self.capturing = False
+            self.graph = graph
+            self.kernels_per_replay = runner.model.ops.launches - launches
+        self.graph.replay()
+        runner.model.ops.launches += self.kernels_per_replay
         return self.logits

@@ -143,3 +143,16 @@ def test_position_past_the_table_is_refused(folders):
     runner.add_request("x")
     with pytest.raises(ValueError, match="exceed"):
         runner.step([StepEntry("x", [1] * (cfg.max_position_embeddings + 1), [0])])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_repeated_portion_shapes_are_replayed(folders, plains, dtype):
+    """Portions of one fixed size: from its second occurrence a step shape runs as a replayed
+    graph; the logits are those of the plain implementation all the same."""
+    model, cfg = engine(folders, "B", dtype)
+    reqs = _requests(cfg.vocab_size, [64, 64, 64, 48], seed=12)
+    steps = schedules.portions(reqs, sizes=(16,))
+    runner = runner_for(model, 16, schedules.tokens_held(steps, 64) // 16, graphs=True)
+    got = schedules.replay(runner, steps)
+    assert runner.graph_steps >= 6 and runner.capture_failures == 0
+    compare(got, plains["B"], reqs, dtype)
