@@ -22,6 +22,8 @@
 // Reference counterparts: kv_gather.cu (twice), a batched SGEMM, mask_add_broadcast.cu,
 // softmax.cu, a batched SGEMM and transposes (src/cuda/model.rs:528-581).  Plain
 // reference: tests/plain_ops.py paged_attention.
+#include <cuda.h>
+
 #include "common.cuh"
 
 #ifndef RV_HD
@@ -72,13 +74,20 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
 // One tile of 64 keys for a warp's 16 packed rows: S = Q K^T, mask, online softmax, O += P V.
 // Rows lane/4 ("a") and lane/4 + 8 ("b") of the warp belong to this thread; a key j counts
 // for row a iff lo_a <= j <= hi_a.
-template <int HD>
+// Element offset of 16-byte chunk `chunk` of row `row` in a tile: padded rows, or dense
+// 128-byte rows whose chunks are XOR-swizzled with the row number as TMA's 128-byte swizzle
+// lays them out (the tile must then start on a 1024-byte boundary and HD must be 64).
+template <int HD, bool SW>
+__device__ __forceinline__ int tile_offset(int row, int chunk) {
+    return SW ? row * HD + ((chunk ^ (row & 7)) << 3) : row * (HD + 8) + (chunk << 3);
+}
+
+template <int HD, bool SW = false>
 __device__ __forceinline__ void attend_tile(const unsigned (&qf)[HD / 16][4], const bf16* kt,
                                             const bf16* vt, int tile_key0, int lane, int lo_a,
                                             int hi_a, int lo_b, int hi_b, float scale_log2,
                                             float& m_a, float& m_b, float& l_a, float& l_b,
                                             float (&o)[HD / 8][4]) {
-    constexpr int LD = HD + 8;
     constexpr int KSTEPS = HD / 16;
     // S = Q K^T for 16 rows x 64 keys
     float s[RV_BN / 8][4];
@@ -89,8 +98,8 @@ __device__ __forceinline__ void attend_tile(const unsigned (&qf)[HD / 16][4], co
 #pragma unroll
         for (int nb = 0; nb < RV_BN / 16; ++nb) {
             unsigned b[4];
-            ldmatrix_x4(b, kt + (nb * 16 + (lane & 7) + (lane >> 4) * 8) * LD + kk * 16 +
-                               ((lane >> 3) & 1) * 8);
+            ldmatrix_x4(b, kt + tile_offset<HD, SW>(nb * 16 + (lane & 7) + (lane >> 4) * 8,
+                                                    kk * 2 + ((lane >> 3) & 1)));
             mma_bf16(s[2 * nb], qf[kk], b[0], b[1]);
             mma_bf16(s[2 * nb + 1], qf[kk], b[2], b[3]);
         }
@@ -146,8 +155,8 @@ __device__ __forceinline__ void attend_tile(const unsigned (&qf)[HD / 16][4], co
 #pragma unroll
         for (int nd = 0; nd < HD / 16; ++nd) {
             unsigned b[4];
-            ldmatrix_x4_trans(b, vt + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LD +
-                                     nd * 16 + (lane >> 4) * 8);
+            ldmatrix_x4_trans(b, vt + tile_offset<HD, SW>(kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8,
+                                                          nd * 2 + (lane >> 4)));
             mma_bf16(o[2 * nd], pa[kk], b[0], b[1]);
             mma_bf16(o[2 * nd + 1], pa[kk], b[2], b[3]);
         }
@@ -338,8 +347,8 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_attention_mma_kernel(
 // key/value head) and one split of 256 keys; its four warps take one tile of 64 keys each,
 // so all four tiles are in flight at once, and their results are combined in warp order in
 // shared memory before the split's partial result is written.
-template <int HD>
-__global__ void __launch_bounds__(128) paged_attention_decode_mma_kernel(
+template <int HD, int NW>
+__global__ void __launch_bounds__(NW * 32) paged_attention_decode_mma_kernel(
     const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ k_cache,
     const bf16* __restrict__ v_cache, const int* __restrict__ block_table, int max_blocks,
     const int* __restrict__ ctx_lens, float* __restrict__ part_o, float2* __restrict__ part_ml,
@@ -349,20 +358,23 @@ __global__ void __launch_bounds__(128) paged_attention_decode_mma_kernel(
     constexpr int CPR = HD / 8;
     constexpr int KSTEPS = HD / 16;
     constexpr int TILE = RV_BN * LD;                   // elements of one K or V tile
+    constexpr int SPLIT = NW * RV_BN;                  // keys per block
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* Qs = (bf16*)smem_raw;                        // [16][LD]
-    bf16* KV = Qs + 16 * LD;                           // [4 warps][K tile, V tile]
+    bf16* KV = Qs + 16 * LD;                           // [NW warps][K tile, V tile]
     const int G = num_heads / num_kv_heads;
     const int r = blockIdx.z;
     const int clen = ctx_lens[r];
     if (clen == 0) return;
     const int tiles_per_head = (G + 15) / 16;
-    const int g = blockIdx.y / tiles_per_head;
-    const int m0 = (blockIdx.y % tiles_per_head) * 16;
-    const int split = blockIdx.x;
+    // the key/value heads of one (request, split) are neighbouring blocks: they run at the same
+    // time and together read whole pages, which are contiguous in memory
+    const int g = blockIdx.x / tiles_per_head;
+    const int m0 = (blockIdx.x % tiles_per_head) * 16;
+    const int split = blockIdx.y;
     const int p = clen - 1;
-    const int key_lo = max(window > 0 ? max(0, p - window + 1) : 0, split * RV_SPLIT);
-    const int key_hi = min(p, split * RV_SPLIT + RV_SPLIT - 1);
+    const int key_lo = max(window > 0 ? max(0, p - window + 1) : 0, split * SPLIT);
+    const int key_hi = min(p, split * SPLIT + SPLIT - 1);
     if (key_lo > key_hi) return;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int page_shift = (page_size & (page_size - 1)) == 0 ? 31 - __clz(page_size) : -1;
@@ -370,13 +382,13 @@ __global__ void __launch_bounds__(128) paged_attention_decode_mma_kernel(
     const size_t kv_row = (size_t)num_kv_heads * HD;
     const int rows = min(16, G - m0);
 
-    for (int c = tid; c < 16 * CPR; c += 128) {
+    for (int c = tid; c < 16 * CPR; c += NW * 32) {
         const int m = c / CPR, ch = c - m * CPR;
         const bool valid = m < rows;
         const bf16* src = q + (size_t)r * q_stride + (size_t)(g * G + m0 + (valid ? m : 0)) * HD + ch * 8;
         cp_async_16(Qs + m * LD + ch * 8, src, valid);
     }
-    const int t = split * (RV_SPLIT / RV_BN) + warp;   // this warp's tile
+    const int t = split * NW + warp;   // this warp's tile
     const bool active = t * RV_BN <= key_hi && t * RV_BN + RV_BN - 1 >= key_lo;
     bf16* kt = KV + warp * 2 * TILE;
     bf16* vt = kt + TILE;
@@ -449,12 +461,12 @@ __global__ void __launch_bounds__(128) paged_attention_decode_mma_kernel(
     }
     __syncthreads();
     const float ln2 = 0.6931471805599453f;
-    for (int i = tid; i < rows * HD; i += 128) {
+    for (int i = tid; i < rows * HD; i += NW * 32) {
         const int m = i / HD, d = i - m * HD;
         float M = -INFINITY;
-        for (int w = 0; w < 4; ++w) M = fmaxf(M, red[((size_t)w * 16 + m) * RS + HD]);
+        for (int w = 0; w < NW; ++w) M = fmaxf(M, red[((size_t)w * 16 + m) * RS + HD]);
         float L = 0.f, O = 0.f;
-        for (int w = 0; w < 4; ++w) {
+        for (int w = 0; w < NW; ++w) {
             const float* src = red + ((size_t)w * 16 + m) * RS;
             const float f = src[HD] == -INFINITY ? 0.f : exp2f(src[HD] - M);
             L += src[HD + 1] * f;
@@ -465,6 +477,328 @@ __global__ void __launch_bounds__(128) paged_attention_decode_mma_kernel(
         if (d == 0) part_ml[slot] = make_float2(M * ln2, L);
     }
 }
+
+
+#if RV_HD == 64
+// ---------------------------------------------------------------------------------
+// Decode as a stream (head size 64, pages of 8, 16, 32 or 64 tokens).  One persistent block
+// per SM: a producer warp brings key and value tiles (64 keys) from the pages into a ring of
+// shared-memory stages with TMA -- one 3-D tensor copy per page, box [page_size tokens, one
+// head, 64 dims], 128-byte swizzle, completion counted on an mbarrier -- and seven consumer
+// warps each own one work item at a time -- (request, key/value head, split of 256 keys) --
+// and walk its four tiles with the online softmax.  Copies stay in flight while other warps
+// compute, and no block-wide barrier or shared-memory merge is needed.  Item i goes to block
+// i % blocks and, there, to consumer (i / blocks) % 7; the producer fills the ring in the
+// order tile 0 of the seven current items, tile 1 of them, and so on, and each consumer takes
+// the ring positions that are its own.  A tile outside its item's keys is passed as an empty
+// stage; a page past the context is zero-filled.  Every mbarrier wait is bounded
+// (RV_STREAM_WAIT_CYCLES clock cycles); when one runs out the thread records a code in `status` and
+// every role leaves its loops.
+#define RV_STREAM_CONSUMERS 7
+#define RV_STREAM_TILES (RV_SPLIT / RV_BN)
+#define RV_STREAM_MAX_STAGES 12
+#define RV_STREAM_WAIT_CYCLES 400000000ll   // about 0.2 s: far beyond any real wait
+
+__device__ __forceinline__ unsigned st_smem_u32(const void* p) {
+    return (unsigned)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void st_mbar_init(unsigned long long* bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(st_smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void st_mbar_arrive(unsigned long long* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(st_smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void st_mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(st_smem_u32(bar)),
+                 "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool st_mbar_try_wait(unsigned long long* bar, unsigned parity) {
+    unsigned done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(st_smem_u32(bar)), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+// Bounded by elapsed clock cycles (a poll may itself block for a while inside the hardware).
+__device__ __forceinline__ bool st_mbar_wait(unsigned long long* bar, unsigned parity,
+                                             volatile int* failed) {
+    const long long start = clock64();
+    while (true) {
+        if (st_mbar_try_wait(bar, parity)) return true;
+        if (*failed || clock64() - start > RV_STREAM_WAIT_CYCLES) return false;
+    }
+}
+// One page of one key/value head: box [page_size, 1, 64] at (dim 0, head, first slot).
+__device__ __forceinline__ void st_tma_page(void* dst, const CUtensorMap* map, int head, int slot0,
+                                            unsigned long long* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(st_smem_u32(dst)), "l"((unsigned long long)map), "r"(st_smem_u32(bar)), "r"(0),
+          "r"(head), "r"(slot0)
+        : "memory");
+}
+
+struct StreamItem {
+    int r, g, m0, split, clen, key_lo, key_hi;   // key range inclusive; key_lo > key_hi: nothing
+};
+
+__device__ __forceinline__ StreamItem stream_item(long long it, long long total, int heads_tiles,
+                                                  int tiles_per_head, int max_splits,
+                                                  const int* __restrict__ ctx_lens, int window) {
+    StreamItem x;
+    x.key_lo = 1;
+    x.key_hi = 0;
+    x.r = x.g = x.m0 = x.split = x.clen = 0;
+    if (it >= total) return x;
+    const int ht = (int)(it % heads_tiles);
+    const long long rest = it / heads_tiles;
+    x.split = (int)(rest % max_splits);
+    x.r = (int)(rest / max_splits);
+    x.g = ht / tiles_per_head;
+    x.m0 = (ht % tiles_per_head) * 16;
+    x.clen = ctx_lens[x.r];
+    if (x.clen == 0) return x;
+    const int p = x.clen - 1;
+    x.key_lo = max(window > 0 ? max(0, p - window + 1) : 0, x.split * RV_SPLIT);
+    x.key_hi = min(p, x.split * RV_SPLIT + RV_SPLIT - 1);
+    return x;
+}
+
+template <int HD>
+__global__ void __launch_bounds__((RV_STREAM_CONSUMERS + 1) * 32, 1)
+paged_attention_decode_stream_kernel(
+    const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+    const bf16* __restrict__ q, int q_stride, const int* __restrict__ block_table, int max_blocks,
+    const int* __restrict__ ctx_lens, float* __restrict__ part_o, float2* __restrict__ part_ml,
+    int max_splits, int num_heads, int num_kv_heads, int page_size, float scale_log2, int window,
+    int n_reqs, int stages, int* __restrict__ status) {
+    rv_pdl_prologue();
+    static_assert(HD == 64, "the stream kernel's stages are 128-byte rows");
+    constexpr int LD = HD + 8;                                      // query rows stay padded
+    constexpr int KSTEPS = HD / 16;
+    constexpr int TILE = RV_BN * HD;                                // dense, swizzled
+    constexpr int NC = RV_STREAM_CONSUMERS;
+    constexpr int MAX_PAGES = RV_SPLIT / 8;                         // pages per item at page size 8
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char* base = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    bf16* ring = (bf16*)base;                                       // [stages][K tile, V tile]
+    bf16* q_slots = ring + (size_t)stages * 2 * TILE;               // [NC][16][LD]
+    __shared__ __align__(8) unsigned long long full_bar[RV_STREAM_MAX_STAGES];
+    __shared__ __align__(8) unsigned long long empty_bar[RV_STREAM_MAX_STAGES];
+    __shared__ volatile int failed;
+    __shared__ volatile unsigned issued;         // ring positions the producer has passed
+    __shared__ int item_info[RV_STREAM_CONSUMERS][6];
+    __shared__ int item_page[RV_STREAM_CONSUMERS][MAX_PAGES];
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int G = num_heads / num_kv_heads;
+    const int tiles_per_head = (G + 15) / 16;
+    const int heads_tiles = num_kv_heads * tiles_per_head;
+    const long long total = (long long)n_reqs * max_splits * heads_tiles;
+    const int nb = gridDim.x, b = blockIdx.x;
+    const long long rounds = (total + (long long)NC * nb - 1) / ((long long)NC * nb);
+    const int page_shift = 31 - __clz(page_size);                   // a power of two (host check)
+    const int pages_per_tile = RV_BN >> page_shift;
+    const int pages_per_item = RV_SPLIT >> page_shift;
+    const unsigned page_bytes = (unsigned)page_size * HD * 2u;
+
+    if (tid == 0) {
+        failed = 0;
+        issued = 0;
+        for (int s = 0; s < stages; ++s) {
+            st_mbar_init(&full_bar[s], 1);
+            st_mbar_init(&empty_bar[s], 1);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+
+    if (warp == NC) {
+        // ---- producer -------------------------------------------------------------------
+        // Per round: the seven items' ranges and the page of every 1/pages_per_item of each
+        // item (all lookups of a round are independent loads), then 4 x 7 tiles of copies.
+        unsigned pos = 0, s = 0, phase = 0;          // ring position, its stage and parity
+        for (long long round = 0; round < rounds && !failed; ++round) {
+            if (lane < NC) {
+                const StreamItem x = stream_item((round * NC + lane) * nb + b, total, heads_tiles,
+                                                 tiles_per_head, max_splits, ctx_lens, window);
+                item_info[lane][0] = x.r;
+                item_info[lane][1] = x.g;
+                item_info[lane][2] = x.split;
+                item_info[lane][3] = x.clen;
+                item_info[lane][4] = x.key_lo;
+                item_info[lane][5] = x.key_hi;
+            }
+            __syncwarp();
+            for (int c = 0; c < NC; ++c) {
+                const int r = item_info[c][0], split = item_info[c][2], clen = item_info[c][3];
+                const bool live = item_info[c][4] <= item_info[c][5];
+                if (lane < pages_per_item) {
+                    const int j0 = split * RV_SPLIT + (lane << page_shift);
+                    int page = -1;
+                    if (live && j0 < clen) page = block_table[(size_t)r * max_blocks + (j0 >> page_shift)];
+                    item_page[c][lane] = page;
+                }
+            }
+            __syncwarp();
+            for (int tile = 0; tile < RV_STREAM_TILES && !failed; ++tile) {
+                for (int c = 0; c < NC; ++c) {
+                    const int g = item_info[c][1], split = item_info[c][2];
+                    const int key_lo = item_info[c][4], key_hi = item_info[c][5];
+                    const int t = split * RV_STREAM_TILES + tile;
+                    const bool active = key_lo <= key_hi && t * RV_BN <= key_hi &&
+                                        t * RV_BN + RV_BN - 1 >= key_lo;
+                    if (pos >= (unsigned)stages && !st_mbar_wait(&empty_bar[s], phase ^ 1u, &failed)) {
+                        if (!failed) { failed = 1; atomicCAS(status, 0, 11); }
+                        break;
+                    }
+                    bf16* kd = ring + (size_t)s * 2 * TILE;
+                    bf16* vd = kd + TILE;
+                    if (!active) {
+                        if (lane == 0) st_mbar_arrive(&full_bar[s]);
+                    } else {
+                        const int page = lane < pages_per_tile
+                                             ? item_page[c][tile * pages_per_tile + lane] : 0;
+                        const unsigned have = __ballot_sync(0xffffffffu, lane < pages_per_tile && page >= 0);
+                        const unsigned miss = __ballot_sync(0xffffffffu, lane < pages_per_tile && page < 0);
+                        if (miss) {                 // pages past the context read as zeros
+                            const uint4 z = make_uint4(0, 0, 0, 0);
+                            for (int pi = 0; pi < pages_per_tile; ++pi) {
+                                if (!((miss >> pi) & 1u)) continue;
+                                uint4* kz = (uint4*)(kd + (size_t)pi * page_size * HD);
+                                uint4* vz = (uint4*)(vd + (size_t)pi * page_size * HD);
+                                for (int i = lane; i < (int)(page_bytes / 16); i += 32) {
+                                    kz[i] = z;
+                                    vz[i] = z;
+                                }
+                            }
+                            __syncwarp();
+                        }
+                        if (lane == 0) st_mbar_expect_tx(&full_bar[s], (unsigned)__popc(have) * 2u * page_bytes);
+                        __syncwarp();
+                        if (lane < pages_per_tile && page >= 0) {
+                            st_tma_page(kd + (size_t)lane * page_size * HD, &map_k, g,
+                                        page << page_shift, &full_bar[s]);
+                            st_tma_page(vd + (size_t)lane * page_size * HD, &map_v, g,
+                                        page << page_shift, &full_bar[s]);
+                        }
+                    }
+                    ++pos;
+                    __syncwarp();
+                    if (lane == 0) issued = pos;
+                    if (++s == (unsigned)stages) { s = 0; phase ^= 1u; }
+                }
+            }
+            __syncwarp();
+        }
+        // No copy may still be in flight when the block returns.  On the normal path the
+        // consumers have waited for every stage; after a failure the producer waits (bounded)
+        // for the stages it armed last.
+        if (failed) {
+            const long long start = clock64();
+            for (int st = 0; st < stages; ++st) {
+                bool done = false;
+                while (!done && clock64() - start < RV_STREAM_WAIT_CYCLES)
+                    done = st_mbar_try_wait(&full_bar[st], st < (int)s ? phase : phase ^ 1u);
+            }
+        }
+    } else {
+        // ---- consumer `warp` -------------------------------------------------------------------
+        const int c = warp;
+        bf16* Qs = q_slots + (size_t)c * 16 * LD;
+        const float ln2 = 0.6931471805599453f;
+        // this consumer's ring positions are c, c + NC, c + 2 NC, ...: stage and parity step along
+        // A parity wait is only meaningful once the stage's previous use has completed, which
+        // holds as soon as the producer has passed this position: the consumer first waits
+        // for that (`issued`), then for the stage's data.
+        unsigned s = (unsigned)c % (unsigned)stages, phase = ((unsigned)c / (unsigned)stages) & 1u;
+        unsigned my_pos = (unsigned)c;
+        for (long long round = 0; round < rounds && !failed; ++round) {
+            const long long it = (round * NC + c) * nb + b;
+            const StreamItem x = stream_item(it, total, heads_tiles, tiles_per_head, max_splits,
+                                             ctx_lens, window);
+            const bool live = x.key_lo <= x.key_hi;
+            const int rows = live ? min(16, G - x.m0) : 0;
+            unsigned qf[KSTEPS][4];
+            if (live) {
+                for (int i = lane; i < 16 * (HD / 8); i += 32) {
+                    const int m = i / (HD / 8), ch = i - m * (HD / 8);
+                    uint4 v = make_uint4(0, 0, 0, 0);
+                    if (m < rows)
+                        v = *(const uint4*)(q + (size_t)x.r * q_stride +
+                                            (size_t)(x.g * G + x.m0 + m) * HD + ch * 8);
+                    *(uint4*)(Qs + m * LD + ch * 8) = v;
+                }
+                __syncwarp();
+#pragma unroll
+                for (int kk = 0; kk < KSTEPS; ++kk)
+                    ldmatrix_x4(qf[kk], Qs + (lane & 15) * LD + kk * 16 + (lane >> 4) * 8);
+                __syncwarp();
+            }
+            const int row_a = x.m0 + (lane >> 2), row_b = row_a + 8;
+            const bool ok_a = live && row_a < G, ok_b = live && row_b < G;
+            const int hi_a = ok_a ? x.key_hi : -1, hi_b = ok_b ? x.key_hi : -1;
+            float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
+            float o[HD / 8][4];
+#pragma unroll
+            for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+            bool ok = true;
+            for (int tile = 0; tile < RV_STREAM_TILES; ++tile) {
+                {
+                    const long long start = clock64();
+                    while ((int)(issued - my_pos) <= 0 && !failed &&
+                           clock64() - start < RV_STREAM_WAIT_CYCLES) {}
+                }
+                if ((int)(issued - my_pos) <= 0 || !st_mbar_wait(&full_bar[s], phase, &failed)) {
+                    if (!failed) { failed = 1; atomicCAS(status, 0, 12); }
+                    ok = false;
+                    break;
+                }
+                const int t = x.split * RV_STREAM_TILES + tile;
+                const bool active = live && t * RV_BN <= x.key_hi && t * RV_BN + RV_BN - 1 >= x.key_lo;
+                if (active) {
+                    const bf16* kt = ring + (size_t)s * 2 * TILE;
+                    attend_tile<HD, true>(qf, kt, kt + TILE, t * RV_BN, lane, x.key_lo, hi_a, x.key_lo,
+                                          hi_b, scale_log2, m_a, m_b, l_a, l_b, o);
+                }
+                __syncwarp();
+                if (lane == 0) st_mbar_arrive(&empty_bar[s]);
+                my_pos += NC;
+                s += NC;                               // the next position of this consumer
+                while (s >= (unsigned)stages) { s -= (unsigned)stages; phase ^= 1u; }
+            }
+            if (!ok || !live) continue;
+            l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
+            l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+            l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
+            l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+            const int col = (lane & 3) * 2;
+            if (ok_a) {
+                const size_t slot = ((size_t)x.r * num_heads + x.g * G + row_a) * max_splits + x.split;
+#pragma unroll
+                for (int i = 0; i < HD / 8; ++i)
+                    *(float2*)(part_o + slot * HD + i * 8 + col) = make_float2(o[i][0], o[i][1]);
+                if ((lane & 3) == 0) part_ml[slot] = make_float2(m_a * ln2, l_a);
+            }
+            if (ok_b) {
+                const size_t slot = ((size_t)x.r * num_heads + x.g * G + row_b) * max_splits + x.split;
+#pragma unroll
+                for (int i = 0; i < HD / 8; ++i)
+                    *(float2*)(part_o + slot * HD + i * 8 + col) = make_float2(o[i][2], o[i][3]);
+                if ((lane & 3) == 0) part_ml[slot] = make_float2(m_b * ln2, l_b);
+            }
+        }
+    }
+    __syncthreads();
+}
+#endif
 
 static thread_local char g_error[512] = "";
 static int fail(const char* msg) {
@@ -542,12 +876,14 @@ extern "C" int RV_SYM(rv_paged_attention_decode_mma)(
     const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* block_table,
     int max_blocks, const int* q_start, const int* ctx_lens, void* scratch, long long scratch_bytes,
     int n_reqs, int max_ctx_len, int num_heads, int num_kv_heads, int page_size, float scale,
-    int window, void* stream) {
+    int window, int split_keys, void* stream) {
     if (n_reqs == 0) return 0;
     if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads || page_size <= 0 ||
         n_reqs < 0)
         return fail("paged_attention_decode_mma: bad sizes");
-    int max_splits = (max_ctx_len + RV_SPLIT - 1) / RV_SPLIT;
+    if (split_keys != 128 && split_keys != 256)
+        return fail("paged_attention_decode_mma: the split is 128 or 256 keys");
+    int max_splits = (max_ctx_len + split_keys - 1) / split_keys;
     if (max_splits < 1) max_splits = 1;
     const size_t slots = (size_t)n_reqs * num_heads * max_splits;
     if ((long long)(slots * RV_HD * 4 + slots * 8) > scratch_bytes)
@@ -557,21 +893,116 @@ extern "C" int RV_SYM(rv_paged_attention_decode_mma)(
     if (n_reqs > 65535 || num_kv_heads * tiles_per_head > 65535)
         return fail("paged_attention_decode_mma: batch too large for one launch");
     static bool configured = false;
-    const size_t smem = (size_t)(16 + 8 * RV_BN) * (RV_HD + 8) * sizeof(bf16);
-    if (!configured && smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(paged_attention_decode_mma_kernel<RV_HD>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    const size_t smem4 = (size_t)(16 + 8 * RV_BN) * (RV_HD + 8) * sizeof(bf16);
+    const size_t smem2 = (size_t)(16 + 4 * RV_BN) * (RV_HD + 8) * sizeof(bf16);
+    if (!configured) {
+        cudaError_t e = cudaSuccess;
+        if (smem4 > 48 * 1024)
+            e = cudaFuncSetAttribute(paged_attention_decode_mma_kernel<RV_HD, 4>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem4);
+        if (e == cudaSuccess && smem2 > 48 * 1024)
+            e = cudaFuncSetAttribute(paged_attention_decode_mma_kernel<RV_HD, 2>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2);
         if (e != cudaSuccess) return fail(cudaGetErrorString(e));
         configured = true;
     }
-    dim3 grid(max_splits, num_kv_heads * tiles_per_head, n_reqs);
+    if (max_splits > 65535) return fail("paged_attention_decode_mma: context too long for one launch");
+    dim3 grid(num_kv_heads * tiles_per_head, max_splits, n_reqs);
     float* part_o = (float*)scratch;
     float2* part_ml = (float2*)((char*)scratch + slots * RV_HD * 4);
-    rv_launch(paged_attention_decode_mma_kernel<RV_HD>, dim3(grid), dim3(128), smem,
-              (cudaStream_t)stream, (const bf16*)q, q_stride, (const bf16*)k_cache,
-              (const bf16*)v_cache, block_table, max_blocks, ctx_lens, part_o, part_ml, max_splits,
-              num_heads, num_kv_heads, page_size, scale * 1.4426950408889634f, window);
+    if (split_keys == 256)
+        rv_launch(paged_attention_decode_mma_kernel<RV_HD, 4>, dim3(grid), dim3(128), smem4,
+                  (cudaStream_t)stream, (const bf16*)q, q_stride, (const bf16*)k_cache,
+                  (const bf16*)v_cache, block_table, max_blocks, ctx_lens, part_o, part_ml,
+                  max_splits, num_heads, num_kv_heads, page_size, scale * 1.4426950408889634f, window);
+    else
+        rv_launch(paged_attention_decode_mma_kernel<RV_HD, 2>, dim3(grid), dim3(64), smem2,
+                  (cudaStream_t)stream, (const bf16*)q, q_stride, (const bf16*)k_cache,
+                  (const bf16*)v_cache, block_table, max_blocks, ctx_lens, part_o, part_ml,
+                  max_splits, num_heads, num_kv_heads, page_size, scale * 1.4426950408889634f, window);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fail(cudaGetErrorString(e));
     return 0;
 }
+
+// Decode as a stream (one persistent block per SM); same scratch layout as
+// rv_paged_attention_decode_mma with a split of 256 keys.  Needs head size 64 and pages of 8,
+// 16, 32 or 64 tokens; `total_slots` = pages * page_size of the cache tensors.  `status`
+// receives a non-zero code when a bounded wait runs out (11: producer, 12: consumer).
+#if RV_HD == 64
+typedef CUresult (*RvEncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                    const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                    const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static int kv_map(CUtensorMap* map, const void* cache, long long total_slots, int num_kv_heads,
+                  int page_size) {
+    static RvEncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qr;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qr) !=
+                cudaSuccess || qr != cudaDriverEntryPointSuccess)
+            return fail("paged_attention_decode_stream: cuTensorMapEncodeTiled is not available");
+        fn = (RvEncodeTiledFn)p;
+    }
+    cuuint64_t dims[3] = {RV_HD, (cuuint64_t)num_kv_heads, (cuuint64_t)total_slots};
+    cuuint64_t strides[2] = {RV_HD * 2, (cuuint64_t)num_kv_heads * RV_HD * 2};
+    cuuint32_t box[3] = {RV_HD, 1, (cuuint32_t)page_size};
+    cuuint32_t elem[3] = {1, 1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(cache), dims, strides,
+                    box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail("paged_attention_decode_stream: cuTensorMapEncodeTiled failed");
+    return 0;
+}
+
+extern "C" int RV_SYM(rv_paged_attention_decode_stream)(
+    const void* q, int q_stride, const void* k_cache, const void* v_cache, long long total_slots,
+    const int* block_table, int max_blocks, const int* ctx_lens, void* scratch,
+    long long scratch_bytes, int n_reqs, int max_ctx_len, int num_heads, int num_kv_heads,
+    int page_size, float scale, int window, int n_sms, int* status, void* stream) {
+    if (n_reqs == 0) return 0;
+    if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads || n_reqs < 0 || n_sms <= 0)
+        return fail("paged_attention_decode_stream: bad sizes");
+    if (page_size != 8 && page_size != 16 && page_size != 32 && page_size != 64)
+        return fail("paged_attention_decode_stream: pages of 8, 16, 32 or 64 tokens only");
+    if (((uintptr_t)k_cache | (uintptr_t)v_cache) % 16)
+        return fail("paged_attention_decode_stream: caches must be 16-byte aligned");
+    int max_splits = (max_ctx_len + RV_SPLIT - 1) / RV_SPLIT;
+    if (max_splits < 1) max_splits = 1;
+    const size_t slots = (size_t)n_reqs * num_heads * max_splits;
+    if ((long long)(slots * RV_HD * 4 + slots * 8) > scratch_bytes)
+        return fail("paged_attention_decode_stream: scratch too small");
+    const int G = num_heads / num_kv_heads;
+    const int tiles_per_head = (G + 15) / 16;
+    const long long total = (long long)n_reqs * max_splits * num_kv_heads * tiles_per_head;
+    const size_t tile_bytes = (size_t)2 * RV_BN * RV_HD * sizeof(bf16);
+    const size_t q_bytes = (size_t)RV_STREAM_CONSUMERS * 16 * (RV_HD + 8) * sizeof(bf16);
+    const size_t budget = 212 * 1024;                 // about 10 KB of static shared memory on top
+    int stages = (int)((budget - 1024 - q_bytes) / tile_bytes);
+    if (stages > RV_STREAM_MAX_STAGES) stages = RV_STREAM_MAX_STAGES;
+    const size_t smem = (size_t)stages * tile_bytes + q_bytes + 1024;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(paged_attention_decode_stream_kernel<RV_HD>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget);
+        if (e != cudaSuccess) return fail(cudaGetErrorString(e));
+        configured = true;
+    }
+    CUtensorMap map_k, map_v;
+    if (kv_map(&map_k, k_cache, total_slots, num_kv_heads, page_size)) return 1;
+    if (kv_map(&map_v, v_cache, total_slots, num_kv_heads, page_size)) return 1;
+    long long blocks = total < n_sms ? total : n_sms;
+    float* part_o = (float*)scratch;
+    float2* part_ml = (float2*)((char*)scratch + slots * RV_HD * 4);
+    rv_launch(paged_attention_decode_stream_kernel<RV_HD>, dim3((unsigned)blocks),
+              dim3((RV_STREAM_CONSUMERS + 1) * 32), smem, (cudaStream_t)stream, map_k, map_v,
+              (const bf16*)q, q_stride, block_table, max_blocks, ctx_lens, part_o, part_ml,
+              max_splits, num_heads, num_kv_heads, page_size, scale * 1.4426950408889634f, window,
+              n_reqs, stages, status);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(cudaGetErrorString(e));
+    return 0;
+}
+#endif

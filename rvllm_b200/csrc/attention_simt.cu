@@ -271,7 +271,8 @@ template <typename T>
 __global__ void paged_attention_merge_kernel(const float* __restrict__ part_o,
                                              const float2* __restrict__ part_ml,
                                              const int* __restrict__ ctx_lens, T* __restrict__ out,
-                                             int max_splits, int num_heads, int hd, int window) {
+                                             int max_splits, int num_heads, int hd, int window,
+                                             int split_keys) {
     rv_pdl_prologue();
     constexpr bool kFast = sizeof(T) == 2;
     const int r = blockIdx.y, h = blockIdx.x;
@@ -283,7 +284,7 @@ __global__ void paged_attention_merge_kernel(const float* __restrict__ part_o,
     }
     const int p = clen - 1;
     const int lo = window > 0 ? max(0, p - window + 1) : 0;
-    const int s0 = lo / RV_ATTN_SPLIT, s1 = p / RV_ATTN_SPLIT;
+    const int s0 = lo / split_keys, s1 = p / split_keys;
     const size_t base = ((size_t)r * num_heads + h) * max_splits;
     float M = -INFINITY;
     for (int s = s0; s <= s1; ++s) M = fmaxf(M, part_ml[base + s].x);
@@ -386,7 +387,7 @@ extern "C" int rv_paged_attention_decode(const void* q, int dtype, int q_stride,
     dim3 mgrid(num_heads, n_reqs);
     RV_DISPATCH_DTYPE(dtype, "paged_attention_merge",
         (rv_launch(paged_attention_merge_kernel<T>, dim3(mgrid), dim3(hd < 32 ? 32 : (hd > 128 ? 128 : ((hd + 31) / 32) * 32)), 0, s, 
-            part_o, part_ml, ctx_lens, (T*)out, max_splits, num_heads, hd, window)));
+            part_o, part_ml, ctx_lens, (T*)out, max_splits, num_heads, hd, window, RV_ATTN_SPLIT)));
     RV_CHECK_LAUNCH("paged_attention_merge");
     return 0;
 }
@@ -395,9 +396,10 @@ extern "C" int rv_paged_attention_decode(const void* q, int dtype, int q_stride,
 // in the same scratch layout.
 extern "C" int rv_paged_attention_merge(const void* scratch, const int* ctx_lens, void* out,
                                         int dtype, int n_reqs, int max_ctx_len, int num_heads,
-                                        int hd, int window, void* stream) {
+                                        int hd, int window, int split_keys, void* stream) {
     if (n_reqs == 0) return 0;
-    int max_splits = (max_ctx_len + RV_ATTN_SPLIT - 1) / RV_ATTN_SPLIT;
+    if (split_keys <= 0) RV_FAIL("paged_attention_merge: bad split size");
+    int max_splits = (max_ctx_len + split_keys - 1) / split_keys;
     if (max_splits < 1) max_splits = 1;
     if (n_reqs < 0 || n_reqs > 65535 || num_heads <= 0 || hd <= 0)
         RV_FAIL("paged_attention_merge: bad sizes");
@@ -408,7 +410,7 @@ extern "C" int rv_paged_attention_merge(const void* scratch, const int* ctx_lens
     const int threads = hd < 32 ? 32 : (hd > 128 ? 128 : ((hd + 31) / 32) * 32);
     RV_DISPATCH_DTYPE(dtype, "paged_attention_merge",
         (rv_launch(paged_attention_merge_kernel<T>, dim3(mgrid), dim3(threads), 0, (cudaStream_t)stream, 
-            part_o, part_ml, ctx_lens, (T*)out, max_splits, num_heads, hd, window)));
+            part_o, part_ml, ctx_lens, (T*)out, max_splits, num_heads, hd, window, split_keys)));
     RV_CHECK_LAUNCH("paged_attention_merge");
     return 0;
 }

@@ -18,7 +18,7 @@
 // in rank order through distributed shared memory (no atomics, no global workspace: the
 // sum is deterministic).  The TMA copies are per block: no multicast.
 //
-// Every wait on an mbarrier is bounded: after RV_SPIN_LIMIT failed polls the thread
+// Every wait on an mbarrier is bounded: after RV_WAIT_CYCLES clock cycles the thread
 // records an error code in `status`, every role leaves its loop, the producer waits
 // (again bounded) for the copies it has in flight, TMEM is freed and the block returns.
 //
@@ -32,7 +32,7 @@
 #define RV_GEMM_BK 64           // K elements per stage: 128 bytes, one swizzle row
 #define RV_GEMM_MAX_STAGES 12
 #define RV_GEMM_SMEM_LIMIT (226 * 1024)
-#define RV_SPIN_LIMIT (1u << 22)
+#define RV_WAIT_CYCLES 400000000ll   // about 0.2 s: far beyond any real wait
 
 typedef __nv_bfloat16 bf16;
 
@@ -59,14 +59,15 @@ __device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned 
         : "memory");
     return done != 0;
 }
-// Bounded wait: false when the limit ran out or another thread already gave up.
+// Bounded wait: false when the time limit ran out or another thread already gave up.  The
+// bound is in clock cycles because a single poll may block for a while inside the hardware.
 __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity,
                                           volatile int* failed) {
-    for (unsigned i = 0; i < RV_SPIN_LIMIT; ++i) {
+    const long long start = clock64();
+    while (true) {
         if (mbar_try_wait(bar, parity)) return true;
-        if (*failed) return false;
+        if (*failed || clock64() - start > RV_WAIT_CYCLES) return false;
     }
-    return false;
 }
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map,
                                             unsigned long long* bar, int c0, int c1) {
@@ -208,7 +209,8 @@ __global__ void __launch_bounds__(128) gemm_tcgen05_kernel(
         for (int i = max(0, issued - stages); i < issued; ++i) {
             const int s = i % stages;
             bool ok = false;
-            for (unsigned n = 0; n < RV_SPIN_LIMIT && !ok; ++n)
+            const long long start = clock64();
+            while (!ok && clock64() - start < RV_WAIT_CYCLES)
                 ok = mbar_try_wait(&full_bar[s], (i / stages) & 1);
             if (!ok && !failed) { failed = 1; atomicCAS(status, 0, 2); }
         }

@@ -56,6 +56,13 @@ class CudaOps:
         # are multiples of 16 up to 128), "simt" = the float32-arithmetic kernels
         self.prefill_attention = os.environ.get("RVLLM_PREFILL_ATTENTION", "mma")
         self.decode_attention = os.environ.get("RVLLM_DECODE_ATTENTION", "mma")
+        # keys per block of the tensor-core decode kernel: 256 (four warps) or 128 (two)
+        self.decode_split = int(os.environ.get("RVLLM_ATTN_DECODE_SPLIT", "256"))
+        # "stream": one persistent block per SM with a producer warp and a ring of stages;
+        # "block": one block per (request, head, split)
+        self.decode_kernel = os.environ.get("RVLLM_ATTN_DECODE_KERNEL", "block")
+        self._sm_count = torch.cuda.get_device_properties(
+            torch.cuda.current_device()).multi_processor_count
         # bfloat16 products with at most `gemm_small_m` tokens go to the tcgen05
         # weight-streaming kernel (gemm_tcgen05.cu), whose weight copies start before the
         # previous kernel has finished; larger ones go to cuBLAS.  RVLLM_GEMM=cublas sends
@@ -150,8 +157,9 @@ class CudaOps:
             code = int(st.item())
             if code != 0:
                 st.zero_()
-                raise KernelError(f"gemm_tcgen05 gave up waiting on an mbarrier (code {code}) "
-                                  f"on {device}; its output is not valid")
+                raise KernelError(f"a kernel gave up waiting on an mbarrier (code {code}: 1-4 "
+                                  f"gemm_tcgen05, 11-12 decode attention) on {device}; its "
+                                  f"output is not valid")
 
     def linear(self, x, w, bias=None, out_dtype=None):
         out_dtype = out_dtype or x.dtype
@@ -295,23 +303,40 @@ class CudaOps:
                                    page_size, scale, window, out, scratch=None):
         """Tensor-core split-KV attention (bfloat16) for requests [0, n_reqs) that bring one
         token each; the splits are combined by the merge kernel."""
+        stream = self.decode_kernel == "stream" and head_dim == 64 and page_size in (8, 16, 32, 64)
+        split = 256 if stream else self.decode_split
         need = self.lib.rv_paged_attention_decode_scratch_bytes(
-            c_int(n_reqs), c_int(num_heads), c_int(head_dim), c_int(max_ctx_len))
+            c_int(n_reqs), c_int(num_heads), c_int(head_dim), c_int(max_ctx_len * (256 // split)))
         if scratch is None:
             scratch = self._scratch_buffer(need, qkv.device)
         lib = self._attn_lib(head_dim)
-        fn = getattr(lib, f"rv_paged_attention_decode_mma_hd{head_dim}")
         win = c_int(window if window else 0)
+        if self.decode_kernel == "stream" and head_dim == 64 and page_size in (8, 16, 32, 64):
+            fn = getattr(lib, f"rv_paged_attention_decode_stream_hd{head_dim}")
+            self._check_attn(lib, head_dim, fn(
+                _ptr(qkv), c_int(qkv.shape[1]), _ptr(k_cache), _ptr(v_cache),
+                c_longlong(k_cache.shape[0] * k_cache.shape[1]), _ptr(block_table),
+                c_int(block_table.shape[1]), _ptr(ctx_lens), _ptr(scratch),
+                c_longlong(scratch.numel() * scratch.element_size()), c_int(n_reqs),
+                c_int(max_ctx_len), c_int(num_heads), c_int(num_kv_heads), c_int(page_size),
+                c_float(scale), win, c_int(self._sm_count), _ptr(self._gemm_status(qkv.device)),
+                self._stream()), "paged_attention_decode_stream")
+            self._check(self.lib.rv_paged_attention_merge(
+                _ptr(scratch), _ptr(ctx_lens), _ptr(out), _code(out.dtype), c_int(n_reqs),
+                c_int(max_ctx_len), c_int(num_heads), c_int(head_dim), win, c_int(256),
+                self._stream()), "paged_attention_merge")
+            return
+        fn = getattr(lib, f"rv_paged_attention_decode_mma_hd{head_dim}")
         self._check_attn(lib, head_dim, fn(
             _ptr(qkv), c_int(qkv.shape[1]), _ptr(k_cache), _ptr(v_cache), _ptr(block_table),
             c_int(block_table.shape[1]), _ptr(q_start), _ptr(ctx_lens), _ptr(scratch),
             c_longlong(scratch.numel() * scratch.element_size()), c_int(n_reqs),
             c_int(max_ctx_len), c_int(num_heads), c_int(num_kv_heads), c_int(page_size),
-            c_float(scale), win, self._stream()), "paged_attention_decode_mma")
+            c_float(scale), win, c_int(split), self._stream()), "paged_attention_decode_mma")
         self._check(self.lib.rv_paged_attention_merge(
             _ptr(scratch), _ptr(ctx_lens), _ptr(out), _code(out.dtype), c_int(n_reqs),
-            c_int(max_ctx_len), c_int(num_heads), c_int(head_dim), win, self._stream()),
-            "paged_attention_merge")
+            c_int(max_ctx_len), c_int(num_heads), c_int(head_dim), win, c_int(split),
+            self._stream()), "paged_attention_merge")
 
     def paged_attention_general(self, qkv, num_heads, num_kv_heads, head_dim, k_cache, v_cache,
                                 ctx, group, scale, window, out):

@@ -186,6 +186,11 @@ ATTN_CASES = [
     ([1, 7, 2, 64], [700, 7, 130, 64], 3, 1, 80, 16, None),
     ([1, 1, 9, 33], [290, 17, 100, 260], 8, 2, 16, 16, 37),
     ([3], [515], 4, 4, 128, 32, None),
+    # head size 64: the decode kernels that stream pages by TMA (pages of 8, 16, 32, 64)
+    ([1, 1, 1, 1, 6], [700, 1, 257, 64, 6], 8, 2, 64, 16, None),
+    ([1, 1, 1, 2], [300, 255, 9, 130], 12, 4, 64, 8, 100),
+    ([1, 1, 1], [1030, 33, 512], 4, 1, 64, 32, None),
+    ([1, 1], [400, 70], 2, 2, 64, 64, 129),
 ]
 
 
