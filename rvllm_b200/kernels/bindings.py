@@ -59,8 +59,12 @@ class CudaOps:
         # keys per block of the tensor-core decode kernel: 256 (four warps) or 128 (two)
         self.decode_split = int(os.environ.get("RVLLM_ATTN_DECODE_SPLIT", "256"))
         # "stream": one persistent block per SM with a producer warp and a ring of stages;
-        # "block": one block per (request, head, split)
-        self.decode_kernel = os.environ.get("RVLLM_ATTN_DECODE_KERNEL", "block")
+        # "block": one block per (request, head, split); "auto": the stream kernel where it
+        # measured faster -- when its work items fill one round of its seven consumer warps
+        # per SM more than half (batch 8 at 4,096 tokens on 148 SMs: 32 us -> 26 us) -- and the
+        # block kernel elsewhere (less work: its fixed cost is lower; more: it keeps more
+        # warps busy per SM)
+        self.decode_kernel = os.environ.get("RVLLM_ATTN_DECODE_KERNEL", "auto")
         self._sm_count = torch.cuda.get_device_properties(
             torch.cuda.current_device()).multi_processor_count
         # bfloat16 products with at most `gemm_small_m` tokens go to the tcgen05
@@ -303,7 +307,12 @@ class CudaOps:
                                    page_size, scale, window, out, scratch=None):
         """Tensor-core split-KV attention (bfloat16) for requests [0, n_reqs) that bring one
         token each; the splits are combined by the merge kernel."""
-        stream = self.decode_kernel == "stream" and head_dim == 64 and page_size in (8, 16, 32, 64)
+        stream = (self.decode_kernel in ("stream", "auto") and head_dim == 64
+                  and page_size in (8, 16, 32, 64))
+        if stream and self.decode_kernel == "auto":
+            items = (n_reqs * -(-max_ctx_len // 256) * num_kv_heads
+                     * -(-(num_heads // num_kv_heads) // 16))
+            stream = 4 * self._sm_count <= items <= 7 * self._sm_count
         split = 256 if stream else self.decode_split
         need = self.lib.rv_paged_attention_decode_scratch_bytes(
             c_int(n_reqs), c_int(num_heads), c_int(head_dim), c_int(max_ctx_len * (256 // split)))
@@ -311,7 +320,7 @@ class CudaOps:
             scratch = self._scratch_buffer(need, qkv.device)
         lib = self._attn_lib(head_dim)
         win = c_int(window if window else 0)
-        if self.decode_kernel == "stream" and head_dim == 64 and page_size in (8, 16, 32, 64):
+        if stream:
             fn = getattr(lib, f"rv_paged_attention_decode_stream_hd{head_dim}")
             self._check_attn(lib, head_dim, fn(
                 _ptr(qkv), c_int(qkv.shape[1]), _ptr(k_cache), _ptr(v_cache),

@@ -211,6 +211,18 @@ def test_paged_attention(ops, dtype, case, standout):
     out = torch.full((ctx.n_tokens, nh * hd), float("nan"), dtype=dtype, device="cuda")
     ops.paged_attention(dq, nh, nkv, hd, dk, dv, dctx, dgroup, scale, window, out)
     assert torch.allclose(out.cpu().float(), ref.float(), **t)
+    if dtype == torch.bfloat16 and hd == 64:
+        # both tensor-core decode kernels by name (the default picks one by the amount of work)
+        chosen = ops.decode_kernel
+        try:
+            for kernel in ("block", "stream"):
+                ops.decode_kernel = kernel
+                out1 = torch.full((ctx.n_tokens, nh * hd), float("nan"), dtype=dtype, device="cuda")
+                ops.paged_attention(dq, nh, nkv, hd, dk, dv, dctx, dgroup, scale, window, out1)
+                assert torch.allclose(out1.cpu().float(), ref.float(), **t), kernel
+            ops.check_status()
+        finally:
+            ops.decode_kernel = chosen
     # every token through the general kernel
     out2 = torch.full((ctx.n_tokens, nh * hd), float("nan"), dtype=dtype, device="cuda")
     ops.paged_attention_general(dq, nh, nkv, hd, dk, dv, dctx, dgroup, scale, window, out2)
