@@ -482,21 +482,20 @@ __global__ void __launch_bounds__(NW * 32) paged_attention_decode_mma_kernel(
 #if RV_HD == 64
 // ---------------------------------------------------------------------------------
 // Decode as a stream (head size 64, pages of 8, 16, 32 or 64 tokens).  One persistent block
-// per SM: a producer warp brings key and value tiles (64 keys) from the pages into a ring of
-// shared-memory stages with TMA -- one 3-D tensor copy per page, box [page_size tokens, one
-// head, 64 dims], 128-byte swizzle, completion counted on an mbarrier -- and seven consumer
-// warps each own one work item at a time -- (request, key/value head, split of 256 keys) --
-// and walk its four tiles with the online softmax.  Copies stay in flight while other warps
-// compute, and no block-wide barrier or shared-memory merge is needed.  Item i goes to block
-// i % blocks and, there, to consumer (i / blocks) % 7; the producer fills the ring in the
-// order tile 0 of the seven current items, tile 1 of them, and so on, and each consumer takes
-// the ring positions that are its own.  A tile outside its item's keys is passed as an empty
-// stage; a page past the context is zero-filled.  Every mbarrier wait is bounded
-// (RV_STREAM_WAIT_CYCLES clock cycles); when one runs out the thread records a code in `status` and
-// every role leaves its loops.
-#define RV_STREAM_CONSUMERS 7
-#define RV_STREAM_TILES (RV_SPLIT / RV_BN)
-#define RV_STREAM_MAX_STAGES 12
+// per SM; each of its six warps is a pipeline of its own.  A warp takes work items --
+// (request, key/value head, split of 128 or 256 keys) -- round robin, brings the item's key
+// and value tiles (64 keys) from the pages into its private ring of two stages with TMA (one
+// 3-D tensor copy per page, box [page_size tokens, one head, 64 dims], 128-byte swizzle,
+// completion counted on an mbarrier of the stage) and walks them with the online softmax.
+// The copy of the next tile -- of the next item, when this one ends -- is in flight while a
+// tile is computed, the block table entries and the context length of the item after the one
+// being loaded are fetched one item ahead, and its query rows arrive by cp.async; so the warp
+// never waits for a chain of dependent loads, and no warp waits for another.  Only tiles
+// that hold keys of the item are copied; a page past the context is zero-filled.  Every
+// mbarrier wait is bounded (RV_STREAM_WAIT_CYCLES clock cycles); when one runs out the warp
+// records code 12 in `status`, waits (bounded) for its copies in flight and leaves.
+#define RV_STREAM_WARPS 6
+#define RV_STREAM_STAGES 2
 #define RV_STREAM_WAIT_CYCLES 400000000ll   // about 0.2 s: far beyond any real wait
 
 __device__ __forceinline__ unsigned st_smem_u32(const void* p) {
@@ -504,9 +503,6 @@ __device__ __forceinline__ unsigned st_smem_u32(const void* p) {
 }
 __device__ __forceinline__ void st_mbar_init(unsigned long long* bar, unsigned count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(st_smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void st_mbar_arrive(unsigned long long* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(st_smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ void st_mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(st_smem_u32(bar)),
@@ -525,12 +521,11 @@ __device__ __forceinline__ bool st_mbar_try_wait(unsigned long long* bar, unsign
     return done != 0;
 }
 // Bounded by elapsed clock cycles (a poll may itself block for a while inside the hardware).
-__device__ __forceinline__ bool st_mbar_wait(unsigned long long* bar, unsigned parity,
-                                             volatile int* failed) {
+__device__ __forceinline__ bool st_mbar_wait(unsigned long long* bar, unsigned parity) {
     const long long start = clock64();
     while (true) {
         if (st_mbar_try_wait(bar, parity)) return true;
-        if (*failed || clock64() - start > RV_STREAM_WAIT_CYCLES) return false;
+        if (clock64() - start > RV_STREAM_WAIT_CYCLES) return false;
     }
 }
 // One page of one key/value head: box [page_size, 1, 64] at (dim 0, head, first slot).
@@ -544,259 +539,235 @@ __device__ __forceinline__ void st_tma_page(void* dst, const CUtensorMap* map, i
         : "memory");
 }
 
-struct StreamItem {
-    int r, g, m0, split, clen, key_lo, key_hi;   // key range inclusive; key_lo > key_hi: nothing
+// What the computing side needs to know of an item whose tiles are on their way.
+struct StreamMeta {
+    int r, g, m0, split, key_lo, key_hi, t_first, t_last;
 };
 
-__device__ __forceinline__ StreamItem stream_item(long long it, long long total, int heads_tiles,
-                                                  int tiles_per_head, int max_splits,
-                                                  const int* __restrict__ ctx_lens, int window) {
-    StreamItem x;
-    x.key_lo = 1;
-    x.key_hi = 0;
-    x.r = x.g = x.m0 = x.split = x.clen = 0;
-    if (it >= total) return x;
-    const int ht = (int)(it % heads_tiles);
-    const long long rest = it / heads_tiles;
-    x.split = (int)(rest % max_splits);
-    x.r = (int)(rest / max_splits);
-    x.g = ht / tiles_per_head;
-    x.m0 = (ht % tiles_per_head) * 16;
-    x.clen = ctx_lens[x.r];
-    if (x.clen == 0) return x;
-    const int p = x.clen - 1;
-    x.key_lo = max(window > 0 ? max(0, p - window + 1) : 0, x.split * RV_SPLIT);
-    x.key_hi = min(p, x.split * RV_SPLIT + RV_SPLIT - 1);
-    return x;
-}
-
 template <int HD>
-__global__ void __launch_bounds__((RV_STREAM_CONSUMERS + 1) * 32, 1)
+__global__ void __launch_bounds__(RV_STREAM_WARPS * 32, 1)
 paged_attention_decode_stream_kernel(
     const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
     const bf16* __restrict__ q, int q_stride, const int* __restrict__ block_table, int max_blocks,
     const int* __restrict__ ctx_lens, float* __restrict__ part_o, float2* __restrict__ part_ml,
-    int max_splits, int num_heads, int num_kv_heads, int page_size, float scale_log2, int window,
-    int n_reqs, int stages, int* __restrict__ status) {
+    int max_splits, int item_tiles, int num_heads, int num_kv_heads, int page_size,
+    float scale_log2, int window, int n_reqs, int* __restrict__ status) {
     rv_pdl_prologue();
     static_assert(HD == 64, "the stream kernel's stages are 128-byte rows");
     constexpr int LD = HD + 8;                                      // query rows stay padded
     constexpr int KSTEPS = HD / 16;
-    constexpr int TILE = RV_BN * HD;                                // dense, swizzled
-    constexpr int NC = RV_STREAM_CONSUMERS;
-    constexpr int MAX_PAGES = RV_SPLIT / 8;                         // pages per item at page size 8
-    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    constexpr int TILE = RV_BN * HD;                                // elements; dense, swizzled
+    constexpr int W = RV_STREAM_WARPS, S = RV_STREAM_STAGES;
+    extern __shared__ __align__(16) unsigned char smem_raw[];      // aligned by hand below
     unsigned char* base = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    bf16* ring = (bf16*)base;                                       // [stages][K tile, V tile]
-    bf16* q_slots = ring + (size_t)stages * 2 * TILE;               // [NC][16][LD]
-    __shared__ __align__(8) unsigned long long full_bar[RV_STREAM_MAX_STAGES];
-    __shared__ __align__(8) unsigned long long empty_bar[RV_STREAM_MAX_STAGES];
-    __shared__ volatile int failed;
-    __shared__ volatile unsigned issued;         // ring positions the producer has passed
-    __shared__ int item_info[RV_STREAM_CONSUMERS][6];
-    __shared__ int item_page[RV_STREAM_CONSUMERS][MAX_PAGES];
+    bf16* ring = (bf16*)base;                                       // [W][S][K tile, V tile]
+    bf16* q_slots = ring + (size_t)W * S * 2 * TILE;                // [W][2][16][LD]
+    __shared__ __align__(8) unsigned long long full_bar[W][S];
+    __shared__ StreamMeta meta_q[W][4];
 
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
     const int G = num_heads / num_kv_heads;
     const int tiles_per_head = (G + 15) / 16;
     const int heads_tiles = num_kv_heads * tiles_per_head;
     const long long total = (long long)n_reqs * max_splits * heads_tiles;
     const int nb = gridDim.x, b = blockIdx.x;
-    const long long rounds = (total + (long long)NC * nb - 1) / ((long long)NC * nb);
     const int page_shift = 31 - __clz(page_size);                   // a power of two (host check)
-    const int pages_per_tile = RV_BN >> page_shift;
-    const int pages_per_item = RV_SPLIT >> page_shift;
+    const int ppt = RV_BN >> page_shift;                            // pages per tile
+    const int ppi = ppt * item_tiles;                               // pages per item (<= 32)
+    const int item_keys = item_tiles * RV_BN;
     const unsigned page_bytes = (unsigned)page_size * HD * 2u;
 
-    if (tid == 0) {
-        failed = 0;
-        issued = 0;
-        for (int s = 0; s < stages; ++s) {
-            st_mbar_init(&full_bar[s], 1);
-            st_mbar_init(&empty_bar[s], 1);
-        }
+    if (lane == 0) {
+        for (int s = 0; s < S; ++s) st_mbar_init(&full_bar[w][s], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    __syncthreads();
+    __syncwarp();
+    bf16* my_ring = ring + (size_t)w * S * 2 * TILE;
+    bf16* my_q = q_slots + (size_t)w * 2 * 16 * LD;
+    const float ln2 = 0.6931471805599453f;
 
-    if (warp == NC) {
-        // ---- producer -------------------------------------------------------------------
-        // Per round: the seven items' ranges and the page of every 1/pages_per_item of each
-        // item (all lookups of a round are independent loads), then 4 x 7 tiles of copies.
-        unsigned pos = 0, s = 0, phase = 0;          // ring position, its stage and parity
-        for (long long round = 0; round < rounds && !failed; ++round) {
-            if (lane < NC) {
-                const StreamItem x = stream_item((round * NC + lane) * nb + b, total, heads_tiles,
-                                                 tiles_per_head, max_splits, ctx_lens, window);
-                item_info[lane][0] = x.r;
-                item_info[lane][1] = x.g;
-                item_info[lane][2] = x.split;
-                item_info[lane][3] = x.clen;
-                item_info[lane][4] = x.key_lo;
-                item_info[lane][5] = x.key_hi;
+    // ---- the loading side -----------------------------------------------------------------
+    long long lk = 0;                 // this warp's next item is number (lk * W + w) * nb + b
+    int n_live = 0;                   // items with keys met so far (index into meta_q and my_q)
+    bool l_more = true;               // items left to look at
+    int l_t = 0, l_last = -1, l_t0 = 0, l_g = 0, l_page = -1;
+    int nx_clen = 0, nx_page = -1;    // context length and this lane's page of item lk, fetched ahead
+    // fetch the length and the block table entries of item `it` (no use of them yet)
+    auto fetch_ahead = [&](long long it) {
+        nx_clen = 0;
+        nx_page = -1;
+        if (it >= total) return;
+        const long long rest = it / heads_tiles;
+        const int split = (int)(rest % max_splits), r = (int)(rest / max_splits);
+        nx_clen = ctx_lens[r];
+        const int blk = ((split * item_keys) >> page_shift) + lane;
+        if (lane < ppi && blk < max_blocks) nx_page = block_table[(size_t)r * max_blocks + blk];
+    };
+    fetch_ahead((lk * W + w) * nb + b);
+    int n_loaded = 0, n_consumed = 0;
+
+    // move to the next item that has keys; false when there is none
+    auto next_load_item = [&]() -> bool {
+        while (l_more) {
+            const long long it = (lk * W + w) * nb + b;
+            if (it >= total) {
+                l_more = false;
+                break;
             }
-            __syncwarp();
-            for (int c = 0; c < NC; ++c) {
-                const int r = item_info[c][0], split = item_info[c][2], clen = item_info[c][3];
-                const bool live = item_info[c][4] <= item_info[c][5];
-                if (lane < pages_per_item) {
-                    const int j0 = split * RV_SPLIT + (lane << page_shift);
-                    int page = -1;
-                    if (live && j0 < clen) page = block_table[(size_t)r * max_blocks + (j0 >> page_shift)];
-                    item_page[c][lane] = page;
-                }
+            const int clen = nx_clen, page = nx_page;
+            ++lk;
+            fetch_ahead((lk * W + w) * nb + b);
+            const int ht = (int)(it % heads_tiles);
+            const long long rest = it / heads_tiles;
+            const int split = (int)(rest % max_splits), r = (int)(rest / max_splits);
+            if (clen == 0) continue;
+            const int p = clen - 1;
+            const int key_lo = max(window > 0 ? max(0, p - window + 1) : 0, split * item_keys);
+            const int key_hi = min(p, split * item_keys + item_keys - 1);
+            if (key_lo > key_hi) continue;
+            const int g = ht / tiles_per_head, m0 = (ht % tiles_per_head) * 16;
+            l_g = g;
+            l_t0 = split * item_tiles;
+            l_t = key_lo / RV_BN;
+            l_last = key_hi / RV_BN;
+            l_page = (lane < ppi && ((split * item_keys + (lane << page_shift)) < clen)) ? page : -1;
+            if (lane == 0) {
+                StreamMeta& m = meta_q[w][n_live & 3];
+                m.r = r; m.g = g; m.m0 = m0; m.split = split;
+                m.key_lo = key_lo; m.key_hi = key_hi; m.t_first = l_t; m.t_last = l_last;
             }
-            __syncwarp();
-            for (int tile = 0; tile < RV_STREAM_TILES && !failed; ++tile) {
-                for (int c = 0; c < NC; ++c) {
-                    const int g = item_info[c][1], split = item_info[c][2];
-                    const int key_lo = item_info[c][4], key_hi = item_info[c][5];
-                    const int t = split * RV_STREAM_TILES + tile;
-                    const bool active = key_lo <= key_hi && t * RV_BN <= key_hi &&
-                                        t * RV_BN + RV_BN - 1 >= key_lo;
-                    if (pos >= (unsigned)stages && !st_mbar_wait(&empty_bar[s], phase ^ 1u, &failed)) {
-                        if (!failed) { failed = 1; atomicCAS(status, 0, 11); }
-                        break;
-                    }
-                    bf16* kd = ring + (size_t)s * 2 * TILE;
-                    bf16* vd = kd + TILE;
-                    if (!active) {
-                        if (lane == 0) st_mbar_arrive(&full_bar[s]);
-                    } else {
-                        const int page = lane < pages_per_tile
-                                             ? item_page[c][tile * pages_per_tile + lane] : 0;
-                        const unsigned have = __ballot_sync(0xffffffffu, lane < pages_per_tile && page >= 0);
-                        const unsigned miss = __ballot_sync(0xffffffffu, lane < pages_per_tile && page < 0);
-                        if (miss) {                 // pages past the context read as zeros
-                            const uint4 z = make_uint4(0, 0, 0, 0);
-                            for (int pi = 0; pi < pages_per_tile; ++pi) {
-                                if (!((miss >> pi) & 1u)) continue;
-                                uint4* kz = (uint4*)(kd + (size_t)pi * page_size * HD);
-                                uint4* vz = (uint4*)(vd + (size_t)pi * page_size * HD);
-                                for (int i = lane; i < (int)(page_bytes / 16); i += 32) {
-                                    kz[i] = z;
-                                    vz[i] = z;
-                                }
-                            }
-                            __syncwarp();
-                        }
-                        if (lane == 0) st_mbar_expect_tx(&full_bar[s], (unsigned)__popc(have) * 2u * page_bytes);
-                        __syncwarp();
-                        if (lane < pages_per_tile && page >= 0) {
-                            st_tma_page(kd + (size_t)lane * page_size * HD, &map_k, g,
-                                        page << page_shift, &full_bar[s]);
-                            st_tma_page(vd + (size_t)lane * page_size * HD, &map_v, g,
-                                        page << page_shift, &full_bar[s]);
-                        }
-                    }
-                    ++pos;
-                    __syncwarp();
-                    if (lane == 0) issued = pos;
-                    if (++s == (unsigned)stages) { s = 0; phase ^= 1u; }
-                }
+            // its query rows, by cp.async into the slot of this item's parity
+            bf16* Qs = my_q + (size_t)(n_live & 1) * 16 * LD;
+            const int rows = min(16, G - m0);
+            for (int i = lane; i < 16 * (HD / 8); i += 32) {
+                const int m = i / (HD / 8), ch = i - m * (HD / 8);
+                const bool valid = m < rows;
+                const bf16* src = q + (size_t)r * q_stride +
+                                  (size_t)(g * G + m0 + (valid ? m : 0)) * HD + ch * 8;
+                cp_async_16(Qs + m * LD + ch * 8, src, valid);
             }
+            cp_async_commit();
+            ++n_live;
             __syncwarp();
+            return true;
         }
-        // No copy may still be in flight when the block returns.  On the normal path the
-        // consumers have waited for every stage; after a failure the producer waits (bounded)
-        // for the stages it armed last.
-        if (failed) {
-            const long long start = clock64();
-            for (int st = 0; st < stages; ++st) {
-                bool done = false;
-                while (!done && clock64() - start < RV_STREAM_WAIT_CYCLES)
-                    done = st_mbar_try_wait(&full_bar[st], st < (int)s ? phase : phase ^ 1u);
-            }
-        }
-    } else {
-        // ---- consumer `warp` -------------------------------------------------------------------
-        const int c = warp;
-        bf16* Qs = q_slots + (size_t)c * 16 * LD;
-        const float ln2 = 0.6931471805599453f;
-        // this consumer's ring positions are c, c + NC, c + 2 NC, ...: stage and parity step along
-        // A parity wait is only meaningful once the stage's previous use has completed, which
-        // holds as soon as the producer has passed this position: the consumer first waits
-        // for that (`issued`), then for the stage's data.
-        unsigned s = (unsigned)c % (unsigned)stages, phase = ((unsigned)c / (unsigned)stages) & 1u;
-        unsigned my_pos = (unsigned)c;
-        for (long long round = 0; round < rounds && !failed; ++round) {
-            const long long it = (round * NC + c) * nb + b;
-            const StreamItem x = stream_item(it, total, heads_tiles, tiles_per_head, max_splits,
-                                             ctx_lens, window);
-            const bool live = x.key_lo <= x.key_hi;
-            const int rows = live ? min(16, G - x.m0) : 0;
-            unsigned qf[KSTEPS][4];
-            if (live) {
-                for (int i = lane; i < 16 * (HD / 8); i += 32) {
-                    const int m = i / (HD / 8), ch = i - m * (HD / 8);
-                    uint4 v = make_uint4(0, 0, 0, 0);
-                    if (m < rows)
-                        v = *(const uint4*)(q + (size_t)x.r * q_stride +
-                                            (size_t)(x.g * G + x.m0 + m) * HD + ch * 8);
-                    *(uint4*)(Qs + m * LD + ch * 8) = v;
+        return false;
+    };
+    // copy the load cursor's tile into the next stage; the stage is free (the caller knows)
+    auto issue_tile = [&]() {
+        const int s = n_loaded % S;
+        bf16* kd = my_ring + (size_t)s * 2 * TILE;
+        bf16* vd = kd + TILE;
+        unsigned long long* bar = &full_bar[w][s];
+        const int src = (l_t - l_t0) * ppt + lane;
+        const int page = __shfl_sync(0xffffffffu, l_page, src & 31);
+        const bool mine = lane < ppt;
+        const unsigned have = __ballot_sync(0xffffffffu, mine && page >= 0);
+        const unsigned miss = __ballot_sync(0xffffffffu, mine && page < 0);
+        if (miss) {                                 // pages past the context read as zeros
+            const uint4 z = make_uint4(0, 0, 0, 0);
+            for (int pi = 0; pi < ppt; ++pi) {
+                if (!((miss >> pi) & 1u)) continue;
+                uint4* kz = (uint4*)(kd + (size_t)pi * page_size * HD);
+                uint4* vz = (uint4*)(vd + (size_t)pi * page_size * HD);
+                for (int i = lane; i < (int)(page_bytes / 16); i += 32) {
+                    kz[i] = z;
+                    vz[i] = z;
                 }
-                __syncwarp();
-#pragma unroll
-                for (int kk = 0; kk < KSTEPS; ++kk)
-                    ldmatrix_x4(qf[kk], Qs + (lane & 15) * LD + kk * 16 + (lane >> 4) * 8);
-                __syncwarp();
-            }
-            const int row_a = x.m0 + (lane >> 2), row_b = row_a + 8;
-            const bool ok_a = live && row_a < G, ok_b = live && row_b < G;
-            const int hi_a = ok_a ? x.key_hi : -1, hi_b = ok_b ? x.key_hi : -1;
-            float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
-            float o[HD / 8][4];
-#pragma unroll
-            for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
-            bool ok = true;
-            for (int tile = 0; tile < RV_STREAM_TILES; ++tile) {
-                {
-                    const long long start = clock64();
-                    while ((int)(issued - my_pos) <= 0 && !failed &&
-                           clock64() - start < RV_STREAM_WAIT_CYCLES) {}
-                }
-                if ((int)(issued - my_pos) <= 0 || !st_mbar_wait(&full_bar[s], phase, &failed)) {
-                    if (!failed) { failed = 1; atomicCAS(status, 0, 12); }
-                    ok = false;
-                    break;
-                }
-                const int t = x.split * RV_STREAM_TILES + tile;
-                const bool active = live && t * RV_BN <= x.key_hi && t * RV_BN + RV_BN - 1 >= x.key_lo;
-                if (active) {
-                    const bf16* kt = ring + (size_t)s * 2 * TILE;
-                    attend_tile<HD, true>(qf, kt, kt + TILE, t * RV_BN, lane, x.key_lo, hi_a, x.key_lo,
-                                          hi_b, scale_log2, m_a, m_b, l_a, l_b, o);
-                }
-                __syncwarp();
-                if (lane == 0) st_mbar_arrive(&empty_bar[s]);
-                my_pos += NC;
-                s += NC;                               // the next position of this consumer
-                while (s >= (unsigned)stages) { s -= (unsigned)stages; phase ^= 1u; }
-            }
-            if (!ok || !live) continue;
-            l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
-            l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
-            l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
-            l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
-            const int col = (lane & 3) * 2;
-            if (ok_a) {
-                const size_t slot = ((size_t)x.r * num_heads + x.g * G + row_a) * max_splits + x.split;
-#pragma unroll
-                for (int i = 0; i < HD / 8; ++i)
-                    *(float2*)(part_o + slot * HD + i * 8 + col) = make_float2(o[i][0], o[i][1]);
-                if ((lane & 3) == 0) part_ml[slot] = make_float2(m_a * ln2, l_a);
-            }
-            if (ok_b) {
-                const size_t slot = ((size_t)x.r * num_heads + x.g * G + row_b) * max_splits + x.split;
-#pragma unroll
-                for (int i = 0; i < HD / 8; ++i)
-                    *(float2*)(part_o + slot * HD + i * 8 + col) = make_float2(o[i][2], o[i][3]);
-                if ((lane & 3) == 0) part_ml[slot] = make_float2(m_b * ln2, l_b);
             }
         }
+        // the stage's earlier reads (ldmatrix) and the zeros above come before the copies
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) st_mbar_expect_tx(bar, (unsigned)__popc(have) * 2u * page_bytes);
+        __syncwarp();
+        if (mine && page >= 0) {
+            st_tma_page(kd + (size_t)lane * page_size * HD, &map_k, l_g, page << page_shift, bar);
+            st_tma_page(vd + (size_t)lane * page_size * HD, &map_v, l_g, page << page_shift, bar);
+        }
+        ++n_loaded;
+        ++l_t;
+    };
+    auto fill = [&]() {
+        while (n_loaded - n_consumed < S) {
+            if (l_t > l_last && !next_load_item()) break;
+            issue_tile();
+        }
+    };
+
+    // ---- the computing side -----------------------------------------------------------------
+    fill();
+    int n_done = 0;                   // items finished (index into meta_q and my_q)
+    bool failed = false;
+    while (n_consumed < n_loaded && !failed) {
+        __syncwarp();
+        const StreamMeta m = meta_q[w][n_done & 3];
+        const int rows = min(16, G - m.m0);
+        unsigned qf[KSTEPS][4];
+        {
+            cp_async_wait<0>();
+            __syncwarp();
+            const bf16* Qs = my_q + (size_t)(n_done & 1) * 16 * LD;
+#pragma unroll
+            for (int kk = 0; kk < KSTEPS; ++kk)
+                ldmatrix_x4(qf[kk], Qs + (lane & 15) * LD + kk * 16 + (lane >> 4) * 8);
+            __syncwarp();
+        }
+        const int row_a = m.m0 + (lane >> 2), row_b = row_a + 8;
+        const bool ok_a = (lane >> 2) < rows, ok_b = (lane >> 2) + 8 < rows;
+        const int hi_a = ok_a ? m.key_hi : -1, hi_b = ok_b ? m.key_hi : -1;
+        float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
+        float o[HD / 8][4];
+#pragma unroll
+        for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+        for (int t = m.t_first; t <= m.t_last; ++t) {
+            const int s = n_consumed % S;
+            if (!st_mbar_wait(&full_bar[w][s], (unsigned)(n_consumed / S) & 1u)) {
+                failed = true;
+                break;
+            }
+            const bf16* kt = my_ring + (size_t)s * 2 * TILE;
+            attend_tile<HD, true>(qf, kt, kt + TILE, t * RV_BN, lane, m.key_lo, hi_a, m.key_lo, hi_b,
+                                  scale_log2, m_a, m_b, l_a, l_b, o);
+            __syncwarp();
+            ++n_consumed;
+            fill();                                 // the freed stage takes the next tile
+        }
+        if (failed) break;
+        l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
+        l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+        l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
+        l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+        const int col = (lane & 3) * 2;
+        if (ok_a) {
+            const size_t slot = ((size_t)m.r * num_heads + m.g * G + row_a) * max_splits + m.split;
+#pragma unroll
+            for (int i = 0; i < HD / 8; ++i)
+                *(float2*)(part_o + slot * HD + i * 8 + col) = make_float2(o[i][0], o[i][1]);
+            if ((lane & 3) == 0) part_ml[slot] = make_float2(m_a * ln2, l_a);
+        }
+        if (ok_b) {
+            const size_t slot = ((size_t)m.r * num_heads + m.g * G + row_b) * max_splits + m.split;
+#pragma unroll
+            for (int i = 0; i < HD / 8; ++i)
+                *(float2*)(part_o + slot * HD + i * 8 + col) = make_float2(o[i][2], o[i][3]);
+            if ((lane & 3) == 0) part_ml[slot] = make_float2(m_b * ln2, l_b);
+        }
+        ++n_done;
     }
-    __syncthreads();
+    if (failed) {
+        // record it, then wait (bounded) for the copies that are still on their way: none may
+        // arrive after the block has left
+        if (lane == 0) atomicCAS(status, 0, 12);
+        const long long start = clock64();
+        for (int i = n_consumed; i < n_loaded; ++i) {
+            bool done = false;
+            while (!done && clock64() - start < RV_STREAM_WAIT_CYCLES)
+                done = st_mbar_try_wait(&full_bar[w][i % S], (unsigned)(i / S) & 1u);
+        }
+        cp_async_wait<0>();
+    }
 }
 #endif
 
@@ -926,9 +897,10 @@ extern "C" int RV_SYM(rv_paged_attention_decode_mma)(
 }
 
 // Decode as a stream (one persistent block per SM); same scratch layout as
-// rv_paged_attention_decode_mma with a split of 256 keys.  Needs head size 64 and pages of 8,
-// 16, 32 or 64 tokens; `total_slots` = pages * page_size of the cache tensors.  `status`
-// receives a non-zero code when a bounded wait runs out (11: producer, 12: consumer).
+// rv_paged_attention_decode_mma with the split that rv_paged_attention_decode_stream_split
+// names (128 or 256 keys: the smaller one when the larger would leave warps without work).
+// Needs head size 64 and pages of 8, 16, 32 or 64 tokens; `total_slots` = pages * page_size
+// of the cache tensors.  `status` receives code 12 when a bounded wait runs out.
 #if RV_HD == 64
 typedef CUresult (*RvEncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                     const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -957,19 +929,31 @@ static int kv_map(CUtensorMap* map, const void* cache, long long total_slots, in
     return 0;
 }
 
+extern "C" int RV_SYM(rv_paged_attention_decode_stream_split)(int n_reqs, int max_ctx_len,
+                                                              int num_heads, int num_kv_heads,
+                                                              int n_sms) {
+    if (num_kv_heads <= 0 || n_sms <= 0) return RV_SPLIT;
+    const int G = num_heads / num_kv_heads;
+    const long long items = (long long)n_reqs * ((max_ctx_len + RV_SPLIT - 1) / RV_SPLIT) *
+                            num_kv_heads * ((G + 15) / 16);
+    return items < 3ll * RV_STREAM_WARPS * n_sms ? RV_SPLIT / 2 : RV_SPLIT;
+}
+
 extern "C" int RV_SYM(rv_paged_attention_decode_stream)(
     const void* q, int q_stride, const void* k_cache, const void* v_cache, long long total_slots,
     const int* block_table, int max_blocks, const int* ctx_lens, void* scratch,
     long long scratch_bytes, int n_reqs, int max_ctx_len, int num_heads, int num_kv_heads,
-    int page_size, float scale, int window, int n_sms, int* status, void* stream) {
+    int page_size, float scale, int window, int split_keys, int n_sms, int* status, void* stream) {
     if (n_reqs == 0) return 0;
     if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads || n_reqs < 0 || n_sms <= 0)
         return fail("paged_attention_decode_stream: bad sizes");
     if (page_size != 8 && page_size != 16 && page_size != 32 && page_size != 64)
         return fail("paged_attention_decode_stream: pages of 8, 16, 32 or 64 tokens only");
-    if (((uintptr_t)k_cache | (uintptr_t)v_cache) % 16)
-        return fail("paged_attention_decode_stream: caches must be 16-byte aligned");
-    int max_splits = (max_ctx_len + RV_SPLIT - 1) / RV_SPLIT;
+    if (split_keys != RV_SPLIT && split_keys != RV_SPLIT / 2)
+        return fail("paged_attention_decode_stream: splits of 128 or 256 keys only");
+    if (((uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)q) % 16 || (q_stride % 8))
+        return fail("paged_attention_decode_stream: caches and query rows must be 16-byte aligned");
+    int max_splits = (max_ctx_len + split_keys - 1) / split_keys;
     if (max_splits < 1) max_splits = 1;
     const size_t slots = (size_t)n_reqs * num_heads * max_splits;
     if ((long long)(slots * RV_HD * 4 + slots * 8) > scratch_bytes)
@@ -977,30 +961,28 @@ extern "C" int RV_SYM(rv_paged_attention_decode_stream)(
     const int G = num_heads / num_kv_heads;
     const int tiles_per_head = (G + 15) / 16;
     const long long total = (long long)n_reqs * max_splits * num_kv_heads * tiles_per_head;
-    const size_t tile_bytes = (size_t)2 * RV_BN * RV_HD * sizeof(bf16);
-    const size_t q_bytes = (size_t)RV_STREAM_CONSUMERS * 16 * (RV_HD + 8) * sizeof(bf16);
-    const size_t budget = 212 * 1024;                 // about 10 KB of static shared memory on top
-    int stages = (int)((budget - 1024 - q_bytes) / tile_bytes);
-    if (stages > RV_STREAM_MAX_STAGES) stages = RV_STREAM_MAX_STAGES;
-    const size_t smem = (size_t)stages * tile_bytes + q_bytes + 1024;
+    const size_t ring_bytes = (size_t)RV_STREAM_WARPS * RV_STREAM_STAGES * 2 * RV_BN * RV_HD * sizeof(bf16);
+    const size_t q_bytes = (size_t)RV_STREAM_WARPS * 2 * 16 * (RV_HD + 8) * sizeof(bf16);
+    const size_t smem = ring_bytes + q_bytes + 1024;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(paged_attention_decode_stream_kernel<RV_HD>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget);
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return fail(cudaGetErrorString(e));
         configured = true;
     }
     CUtensorMap map_k, map_v;
     if (kv_map(&map_k, k_cache, total_slots, num_kv_heads, page_size)) return 1;
     if (kv_map(&map_v, v_cache, total_slots, num_kv_heads, page_size)) return 1;
-    long long blocks = total < n_sms ? total : n_sms;
+    long long blocks = (total + RV_STREAM_WARPS - 1) / RV_STREAM_WARPS;
+    if (blocks > n_sms) blocks = n_sms;
     float* part_o = (float*)scratch;
     float2* part_ml = (float2*)((char*)scratch + slots * RV_HD * 4);
     rv_launch(paged_attention_decode_stream_kernel<RV_HD>, dim3((unsigned)blocks),
-              dim3((RV_STREAM_CONSUMERS + 1) * 32), smem, (cudaStream_t)stream, map_k, map_v,
+              dim3(RV_STREAM_WARPS * 32), smem, (cudaStream_t)stream, map_k, map_v,
               (const bf16*)q, q_stride, block_table, max_blocks, ctx_lens, part_o, part_ml,
-              max_splits, num_heads, num_kv_heads, page_size, scale * 1.4426950408889634f, window,
-              n_reqs, stages, status);
+              max_splits, split_keys / RV_BN, num_heads, num_kv_heads, page_size,
+              scale * 1.4426950408889634f, window, n_reqs, status);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fail(cudaGetErrorString(e));
     return 0;

@@ -126,22 +126,11 @@ __device__ __forceinline__ float ld_cluster_f32(const float* local, unsigned ran
     return v;
 }
 
-// Timeline of a launch (optional): eight nanosecond stamps per block -- 0 entry, 1 ring filled,
-// 2 previous kernel done, 3 last copy issued, 4 first stage arrived, 5 last MMA committed,
-// 6 accumulator complete, 7 exit.
-__device__ __forceinline__ void stamp(unsigned long long* trace, int j) {
-    if (trace) {
-        unsigned long long t;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-        trace[((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 8 + j] = t;
-    }
-}
-
 template <typename TO>
 __global__ void __launch_bounds__(128) gemm_tcgen05_kernel(
     const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
     TO* __restrict__ out, int* __restrict__ status, int M, int N, int kblocks, int n_pad,
-    int stages, unsigned long long* __restrict__ trace) {
+    int stages) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // the dynamic segment is aligned by hand: swizzled tiles need 1024-byte alignment
     unsigned char* base = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -188,7 +177,6 @@ __global__ void __launch_bounds__(128) gemm_tcgen05_kernel(
 
     if (warp == 0 && lane == 0) {
         // ---- producer: TMA copies of W and x tiles ------------------------------------
-        stamp(trace, 0);
         const unsigned tx = (unsigned)(w_bytes + x_bytes);
         // fill the ring with weight tiles before waiting for the previous kernel: they
         // stream from HBM while it is still running
@@ -198,9 +186,7 @@ __global__ void __launch_bounds__(128) gemm_tcgen05_kernel(
             tma_load_2d(w_tiles + i * w_bytes, &map_w, &full_bar[i], (kb0 + i) * RV_GEMM_BK,
                         tile * RV_GEMM_BM);
         }
-        stamp(trace, 1);
         rv_pdl_wait();
-        stamp(trace, 2);
         for (int i = 0; i < pre; ++i)
             tma_load_2d(x_tiles + i * x_bytes, &map_x, &full_bar[i], (kb0 + i) * RV_GEMM_BK, 0);
         int issued = pre;
@@ -219,7 +205,6 @@ __global__ void __launch_bounds__(128) gemm_tcgen05_kernel(
             tma_load_2d(x_tiles + s * x_bytes, &map_x, &full_bar[s], (kb0 + i) * RV_GEMM_BK, 0);
             issued = i + 1;
         }
-        stamp(trace, 3);
         // no copy of this block may still be in flight when it returns
         for (int i = max(0, issued - stages); i < issued; ++i) {
             const int s = i % stages;
@@ -242,7 +227,6 @@ __global__ void __launch_bounds__(128) gemm_tcgen05_kernel(
                 break;
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            if (i == 0) stamp(trace, 4);
             const unsigned long long a0 = smem_desc_sw128(w_tiles + s * w_bytes);
             const unsigned long long b0 = smem_desc_sw128(x_tiles + s * x_bytes);
 #pragma unroll
@@ -251,7 +235,6 @@ __global__ void __launch_bounds__(128) gemm_tcgen05_kernel(
             tcgen05_commit(&empty_bar[s]);                  // frees the stage when the MMAs are done
         }
         tcgen05_commit(&accum_bar);                         // arrives when every MMA above is done
-        stamp(trace, 5);
     }
     __syncwarp();
     rv_pdl_wait();            // before any thread writes y: the previous kernel is done
@@ -260,7 +243,6 @@ __global__ void __launch_bounds__(128) gemm_tcgen05_kernel(
     bool have = mbar_wait(&accum_bar, 0, &failed);
     if (!have && !failed) { failed = 1; atomicCAS(status, 0, 4); }
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (tid == 0) stamp(trace, 6);
     __syncthreads();          // `failed` is final; the producer has drained its copies
     const bool good = !failed;
     const int n_local = warp * 32 + lane;
@@ -288,10 +270,7 @@ __global__ void __launch_bounds__(128) gemm_tcgen05_kernel(
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
                      "r"(tmem_cols));
     }
-    if (splits == 1) {
-        if (tid == 0) stamp(trace, 7);
-        return;
-    }
+    if (splits == 1) return;
 
     // ---- every block of the cluster adds its share of token rows, in rank order ----------
     cluster_sync_all();                                       // all partial tiles are parked
@@ -304,7 +283,6 @@ __global__ void __launch_bounds__(128) gemm_tcgen05_kernel(
         }
     }
     cluster_sync_all();                                       // nobody leaves while it is read
-    if (tid == 0) stamp(trace, 7);
 }
 
 // ---- host side ----------------------------------------------------------------------------
@@ -402,24 +380,6 @@ extern "C" int rv_gemm_tcgen05_init() {
     return 0;
 }
 
-// Timeline buffer: `rv_gemm_tcgen05_trace(buffer, launches, blocks)` makes the following
-// launches write their stamps to buffer[launch][block][8] (launches beyond `launches` and
-// launches of more than `blocks` blocks are not traced); a null buffer ends it.  A launch
-// recorded into a CUDA graph keeps its slice, so the stamps of the last replay can be read.
-static unsigned long long* g_trace = nullptr;
-static int g_trace_launches = 0, g_trace_blocks = 0, g_trace_next = 0;
-extern "C" void rv_gemm_tcgen05_trace(void* buffer, int launches, int blocks) {
-    g_trace = (unsigned long long*)buffer;
-    g_trace_launches = launches;
-    g_trace_blocks = blocks;
-    g_trace_next = 0;
-}
-extern "C" int rv_gemm_tcgen05_traced() { return g_trace_next; }
-static unsigned long long* next_trace_slice(int blocks) {
-    if (!g_trace || g_trace_next >= g_trace_launches || blocks > g_trace_blocks) return nullptr;
-    return g_trace + (size_t)(g_trace_next++) * g_trace_blocks * 8;
-}
-
 template <typename TO>
 static int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, void* out, int* status, int M,
                   int N, int kblocks, int n_pad, int stages, int tiles, int splits, size_t smem,
@@ -439,8 +399,7 @@ static int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, void* out,
     cfg.attrs = attr;
     cfg.numAttrs = 2;
     cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<TO>, map_w, map_x, (TO*)out, status,
-                                       M, N, kblocks, n_pad, stages,
-                                       next_trace_slice(tiles * splits));
+                                       M, N, kblocks, n_pad, stages);
     if (e != cudaSuccess) RV_FAIL("gemm_tcgen05: %s", cudaGetErrorString(e));
     return 0;
 }

@@ -58,13 +58,11 @@ class CudaOps:
         self.decode_attention = os.environ.get("RVLLM_DECODE_ATTENTION", "mma")
         # keys per block of the tensor-core decode kernel: 256 (four warps) or 128 (two)
         self.decode_split = int(os.environ.get("RVLLM_ATTN_DECODE_SPLIT", "256"))
-        # "stream": one persistent block per SM with a producer warp and a ring of stages;
-        # "block": one block per (request, head, split); "auto": the stream kernel where it
-        # measured faster -- when its work items fill one round of its seven consumer warps
-        # per SM more than half (batch 8 at 4,096 tokens on 148 SMs: 32 us -> 26 us) -- and the
-        # block kernel elsewhere (less work: its fixed cost is lower; more: it keeps more
-        # warps busy per SM)
+        # "stream": one persistent block per SM whose warps each stream their work items'
+        # tiles through a private ring; "block": one block per (request, head, split);
+        # "auto": the stream kernel from `stream_min_items` work items of 256 keys on
         self.decode_kernel = os.environ.get("RVLLM_ATTN_DECODE_KERNEL", "auto")
+        self.stream_min_items = int(os.environ.get("RVLLM_ATTN_STREAM_MIN_ITEMS", "384"))
         self._sm_count = torch.cuda.get_device_properties(
             torch.cuda.current_device()).multi_processor_count
         # bfloat16 products with at most `gemm_small_m` tokens go to the tcgen05
@@ -165,6 +163,15 @@ class CudaOps:
                                   f"gemm_tcgen05, 11-12 decode attention) on {device}; its "
                                   f"output is not valid")
 
+    def _small_product(self, x, w, out_dtype) -> bool:
+        """Whether x . w^T goes to the tcgen05 weight-streaming kernel."""
+        return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+                and 0 < x.shape[0] <= self.gemm_small_m and self.gemm_mode != "cublas"
+                and x.shape[1] % 8 == 0 and x.is_contiguous() and w.is_contiguous()
+                and out_dtype in (torch.bfloat16, torch.float32)
+                and (self.gemm_mode == "tcgen05"
+                     or (w.shape[0] <= 18 * 128 and x.shape[1] >= 4096)))
+
     def linear(self, x, w, bias=None, out_dtype=None):
         out_dtype = out_dtype or x.dtype
         if x.dtype != w.dtype:
@@ -173,12 +180,7 @@ class CudaOps:
             x, w = x.to(wide), w.to(wide)
         if x.shape[0] == 0:
             return torch.empty((0, w.shape[0]), dtype=out_dtype, device=x.device)
-        if (x.dtype == torch.bfloat16 and 0 < x.shape[0] <= self.gemm_small_m
-                and self.gemm_mode != "cublas"
-                and x.shape[1] % 8 == 0 and x.is_contiguous() and w.is_contiguous()
-                and out_dtype in (torch.bfloat16, torch.float32)
-                and (self.gemm_mode == "tcgen05"
-                     or (w.shape[0] <= 18 * 128 and x.shape[1] >= 4096))):
+        if self._small_product(x, w, out_dtype):
             y = self.linear_tcgen05(x, w, out_dtype)
         elif out_dtype == x.dtype:
             y = torch.mm(x, w.t())
@@ -309,16 +311,21 @@ class CudaOps:
         token each; the splits are combined by the merge kernel."""
         stream = (self.decode_kernel in ("stream", "auto") and head_dim == 64
                   and page_size in (8, 16, 32, 64))
+        lib = self._attn_lib(head_dim)
         if stream and self.decode_kernel == "auto":
             items = (n_reqs * -(-max_ctx_len // 256) * num_kv_heads
                      * -(-(num_heads // num_kv_heads) // 16))
-            stream = 4 * self._sm_count <= items <= 7 * self._sm_count
-        split = 256 if stream else self.decode_split
+            stream = items >= self.stream_min_items
+        if stream:
+            split = getattr(lib, f"rv_paged_attention_decode_stream_split_hd{head_dim}")(
+                c_int(n_reqs), c_int(max_ctx_len), c_int(num_heads), c_int(num_kv_heads),
+                c_int(self._sm_count))
+        else:
+            split = self.decode_split
         need = self.lib.rv_paged_attention_decode_scratch_bytes(
             c_int(n_reqs), c_int(num_heads), c_int(head_dim), c_int(max_ctx_len * (256 // split)))
         if scratch is None:
             scratch = self._scratch_buffer(need, qkv.device)
-        lib = self._attn_lib(head_dim)
         win = c_int(window if window else 0)
         if stream:
             fn = getattr(lib, f"rv_paged_attention_decode_stream_hd{head_dim}")
@@ -328,11 +335,12 @@ class CudaOps:
                 c_int(block_table.shape[1]), _ptr(ctx_lens), _ptr(scratch),
                 c_longlong(scratch.numel() * scratch.element_size()), c_int(n_reqs),
                 c_int(max_ctx_len), c_int(num_heads), c_int(num_kv_heads), c_int(page_size),
-                c_float(scale), win, c_int(self._sm_count), _ptr(self._gemm_status(qkv.device)),
-                self._stream()), "paged_attention_decode_stream")
+                c_float(scale), win, c_int(split), c_int(self._sm_count),
+                _ptr(self._gemm_status(qkv.device)), self._stream()),
+                "paged_attention_decode_stream")
             self._check(self.lib.rv_paged_attention_merge(
                 _ptr(scratch), _ptr(ctx_lens), _ptr(out), _code(out.dtype), c_int(n_reqs),
-                c_int(max_ctx_len), c_int(num_heads), c_int(head_dim), win, c_int(256),
+                c_int(max_ctx_len), c_int(num_heads), c_int(head_dim), win, c_int(split),
                 self._stream()), "paged_attention_merge")
             return
         fn = getattr(lib, f"rv_paged_attention_decode_mma_hd{head_dim}")

@@ -349,3 +349,4 @@ def test_gemm_tcgen05(ops, M, N, K, out_dtype):
     y1 = ops.linear_tcgen05(x[:1].contiguous().cuda(), w.cuda(), torch.float32)
     yM = ops.linear_tcgen05(x.cuda(), w.cuda(), torch.float32)
     assert torch.equal(y1[0], yM[0])
+
