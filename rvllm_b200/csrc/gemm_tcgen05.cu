@@ -63,10 +63,12 @@ __device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned 
 // bound is in clock cycles because a single poll may block for a while inside the hardware.
 __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity,
                                           volatile int* failed) {
+    if (mbar_try_wait(bar, parity)) return true;             // the common case: no clock read
     const long long start = clock64();
-    while (true) {
+    for (unsigned i = 1;; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
-        if (*failed || clock64() - start > RV_WAIT_CYCLES) return false;
+        if (*failed) return false;
+        if ((i & 63u) == 0 && clock64() - start > RV_WAIT_CYCLES) return false;
     }
 }
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map,
