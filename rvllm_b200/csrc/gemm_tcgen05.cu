@@ -237,15 +237,21 @@ __global__ void __launch_bounds__(128) gemm_tcgen05_kernel(
             tcgen05_commit(&empty_bar[s]);                  // frees the stage when the MMAs are done
         }
         tcgen05_commit(&accum_bar);                         // arrives when every MMA above is done
+        // this thread alone polls for the accumulator; the other 127 sleep at the block
+        // barrier below instead of competing with the two working threads for issue slots
+        if (!failed && !mbar_wait(&accum_bar, 0, &failed) && !failed) {
+            failed = 1;
+            atomicCAS(status, 0, 4);
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     }
     __syncwarp();
     rv_pdl_wait();            // before any thread writes y: the previous kernel is done
 
     // ---- epilogue: all four warps, warp w owns TMEM lanes [32w, 32w + 32) -------------------
-    bool have = mbar_wait(&accum_bar, 0, &failed);
-    if (!have && !failed) { failed = 1; atomicCAS(status, 0, 4); }
+    __syncthreads();          // the accumulator is complete, `failed` is final, the producer
+                              // has drained its copies
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    __syncthreads();          // `failed` is final; the producer has drained its copies
     const bool good = !failed;
     const int n_local = warp * 32 + lane;
     const int n = tile * RV_GEMM_BM + n_local;                // this thread's output column
