@@ -52,9 +52,11 @@ class CudaOps:
         self._scratch = {}
         self._attn_libs = {}
         self._verbose_build = verbose_build
-        # bfloat16 attention: "mma" = tensor-core kernels (attention_mma.cu, head sizes that
-        # are multiples of 16 up to 128), "simt" = the float32-arithmetic kernels
-        self.prefill_attention = os.environ.get("RVLLM_PREFILL_ATTENTION", "mma")
+        # bfloat16 attention: "mma" = mma.sync tensor-core kernels (attention_mma.cu, head
+        # sizes that are multiples of 16 up to 128), "simt" = the float32-arithmetic kernels;
+        # prompt portions also "tcgen05" (attention_tcgen05.cu, head size 64) and "auto" =
+        # tcgen05 where it applies, else mma
+        self.prefill_attention = os.environ.get("RVLLM_PREFILL_ATTENTION", "auto")
         self.decode_attention = os.environ.get("RVLLM_DECODE_ATTENTION", "mma")
         # keys per block of the tensor-core decode kernel: 256 (four warps) or 128 (two)
         self.decode_split = int(os.environ.get("RVLLM_ATTN_DECODE_SPLIT", "256"))
@@ -160,7 +162,7 @@ class CudaOps:
             if code != 0:
                 st.zero_()
                 raise KernelError(f"a kernel gave up waiting on an mbarrier (code {code}: 1-4 "
-                                  f"gemm_tcgen05, 11-12 decode attention) on {device}; its "
+                                  f"gemm_tcgen05, 12 decode attention, 21 prefill attention) on {device}; its "
                                   f"output is not valid")
 
     def _small_product(self, x, w, out_dtype) -> bool:
@@ -239,6 +241,46 @@ class CudaOps:
             self._attn_libs[head_dim] = lib
         return lib
 
+    def _attn5_lib(self, head_dim: int):
+        """The tcgen05 prefill attention library for this head size, built at first use."""
+        key = ("tcgen05", head_dim)
+        lib = self._attn_libs.get(key)
+        if lib is None:
+            path = build_variant("attention_tcgen05.cu", {"RV_HD": head_dim},
+                                 f"attn5_hd{head_dim}", verbose=self._verbose_build)
+            try:
+                lib = ctypes.CDLL(path)
+            except OSError as e:
+                raise KernelError(f"cannot load the kernel library {path}: {e}") from None
+            getattr(lib, f"rv_attention_tcgen05_last_error_hd{head_dim}").restype = ctypes.c_char_p
+            self._attn_libs[key] = lib
+        return lib
+
+    def _tcgen05_prefill_ok(self, qkv, out, num_heads, num_kv_heads, head_dim, page_size) -> bool:
+        return (qkv.dtype == torch.bfloat16 and head_dim == 64
+                and page_size in (8, 16, 32, 64) and num_heads // num_kv_heads <= 128
+                and qkv.shape[1] % head_dim == 0 and qkv.data_ptr() % 16 == 0
+                and out.data_ptr() % 16 == 0)
+
+    def paged_attention_prefill_tcgen05(self, qkv, num_heads, num_kv_heads, head_dim, k_cache,
+                                        v_cache, ctx, group, scale, window, out):
+        """Requests [n_decode, n_reqs) -- the ones that bring more than one token -- on the
+        tcgen05 kernel (bfloat16, head size 64)."""
+        lib = self._attn5_lib(head_dim)
+        nd = ctx.n_decode
+        fn = getattr(lib, f"rv_paged_attention_prefill_tcgen05_hd{head_dim}")
+        rc = fn(_ptr(qkv), c_int(qkv.shape[1]), c_int(qkv.shape[0]), _ptr(k_cache), _ptr(v_cache),
+                c_longlong(k_cache.shape[0] * k_cache.shape[1]), _ptr(group.block_table),
+                c_int(group.max_blocks), _ptr(ctx.q_start), _ptr(ctx.ctx_lens), _ptr(out),
+                c_int(nd), c_int(ctx.n_reqs - nd), c_int(ctx.max_q_len), c_int(num_heads),
+                c_int(num_kv_heads), c_int(group.page_size), c_float(scale),
+                c_int(window if window else 0), _ptr(self._gemm_status(qkv.device)),
+                self._stream())
+        self.launches += 1
+        if rc != 0:
+            msg = getattr(lib, f"rv_attention_tcgen05_last_error_hd{head_dim}")().decode()
+            raise KernelError(f"paged_attention_prefill_tcgen05: {msg}")
+
     def _check_attn(self, lib, head_dim: int, rc: int, what: str) -> None:
         self.launches += 1
         if rc != 0:
@@ -269,7 +311,12 @@ class CudaOps:
                 self.paged_attention_decode(qkv, num_heads, num_kv_heads, head_dim, k_cache,
                                             v_cache, group.block_table, ctx.ctx_lens, nd,
                                             ctx.max_ctx_len, group.page_size, scale, window, out)
-        if ctx.n_tokens > nd and mma and self.prefill_attention == "mma":
+        if (ctx.n_tokens > nd and self.prefill_attention in ("auto", "tcgen05")
+                and self._tcgen05_prefill_ok(qkv, out, num_heads, num_kv_heads, head_dim,
+                                             group.page_size)):
+            self.paged_attention_prefill_tcgen05(qkv, num_heads, num_kv_heads, head_dim, k_cache,
+                                                 v_cache, ctx, group, scale, window, out)
+        elif ctx.n_tokens > nd and mma and self.prefill_attention in ("auto", "mma", "tcgen05"):
             lib = self._attn_lib(head_dim)
             fn = getattr(lib, f"rv_paged_attention_prefill_mma_hd{head_dim}")
             self._check_attn(lib, head_dim, fn(

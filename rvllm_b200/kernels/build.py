@@ -36,7 +36,7 @@ _variant_locks = {}
 
 
 # Sources compiled on demand with a size baked in, each into a library of its own.
-VARIANT_SOURCES = {"attention_mma.cu"}
+VARIANT_SOURCES = {"attention_mma.cu", "attention_tcgen05.cu"}
 
 
 def sources() -> List[str]:

@@ -350,3 +350,57 @@ def test_gemm_tcgen05(ops, M, N, K, out_dtype):
     yM = ops.linear_tcgen05(x.cuda(), w.cuda(), torch.float32)
     assert torch.equal(y1[0], yM[0])
 
+
+
+PREFILL_CASES = [
+    # q_lens, ctx_lens, heads, kv heads, head size, page size, window.  Head size 64: the
+    # tcgen05 kernel (128 rows = tokens x heads of a group, tiles of 64 keys): group sizes
+    # that do and do not divide 128, one head per group, portions that start in the middle of
+    # a context and end inside a tile or a page, several tiles, a window, every page size.
+    ([40], [40], 4, 1, 64, 16, None),
+    ([128, 3], [128, 3], 8, 2, 64, 16, None),
+    ([130], [130], 8, 2, 64, 16, None),
+    ([70, 5, 200], [170, 5, 500], 12, 4, 64, 8, None),
+    ([33, 64], [400, 64], 6, 2, 64, 32, 100),
+    ([50, 2], [50, 700], 3, 3, 64, 64, None),
+    ([300], [1000], 5, 1, 64, 16, 257),
+    ([257], [257], 1, 1, 64, 16, None),
+]
+
+
+@pytest.mark.parametrize("case", PREFILL_CASES)
+@pytest.mark.parametrize("standout", [False, True])
+def test_prefill_attention_kernels(ops, case, standout):
+    """Prompt portions through each bfloat16 prefill kernel by name."""
+    q_lens, ctx_lens, nh, nkv, hd, ps, window = case
+    g = torch.Generator().manual_seed(21)
+    q, kc, vc, ctx, group = attention_case(torch.bfloat16, g, q_lens, ctx_lens, nh, nkv, hd, ps,
+                                           window, standout)
+    scale = 1.0 / math.sqrt(hd)
+    ref = torch.zeros(ctx.n_tokens, nh * hd, dtype=torch.bfloat16)
+    PlainOps().paged_attention(q, nh, nkv, hd, kc, vc, ctx, group, scale, window, ref)
+    dq, dk, dv, dctx, dgroup = q.cuda(), kc.cuda(), vc.cuda(), to_cuda(ctx), to_cuda(group)
+    chosen = ops.prefill_attention
+    try:
+        for kernel in ("tcgen05", "mma", "simt"):
+            ops.prefill_attention = kernel
+            out = torch.full((ctx.n_tokens, nh * hd), float("nan"), dtype=torch.bfloat16,
+                             device="cuda")
+            ops.paged_attention(dq, nh, nkv, hd, dk, dv, dctx, dgroup, scale, window, out)
+            ops.check_status()
+            assert torch.allclose(out.cpu().float(), ref.float(), atol=2e-2, rtol=2e-2), kernel
+    finally:
+        ops.prefill_attention = chosen
+
+
+def test_prefill_attention_tcgen05_is_used(ops):
+    """The default choice takes the tcgen05 kernel where it applies (its launch is counted by
+    its own library) and refuses nothing it cannot do: other head sizes go to the mma kernel."""
+    g = torch.Generator().manual_seed(22)
+    for hd, expect in ((64, True), (32, False)):
+        q, kc, vc, ctx, group = attention_case(torch.bfloat16, g, [20], [20], 4, 2, hd, 16)
+        out = torch.empty(20, 4 * hd, dtype=torch.bfloat16, device="cuda")
+        assert ops._tcgen05_prefill_ok(q.cuda(), out, 4, 2, hd, 16) is expect
+        ops.paged_attention(q.cuda(), 4, 2, hd, kc.cuda(), vc.cuda(), to_cuda(ctx), to_cuda(group),
+                            0.2, None, out)
+        assert torch.isfinite(out).all()
