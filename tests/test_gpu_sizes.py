@@ -69,3 +69,29 @@ def test_real_sizes_against_plain(setup, dtype, bound):
                     assert int(got[(rid, p)].argmax()) == int(ref[p].argmax()), (name, rid, p)
     model.ops.check_status()
     print(f"{dtype}: worst relative error {worst:.2e}")
+
+
+@pytest.mark.parametrize("decode_kernel,prefill_kernel", [("stream", "tcgen05"), ("block", "mma")])
+def test_real_sizes_each_attention_kernel(setup, decode_kernel, prefill_kernel):
+    """The same in bfloat16 with the attention kernels named instead of chosen by size: the
+    short test contexts would otherwise never reach the stream decode kernel."""
+    from rvllm_b200.engine import ModelRunner, load_model, make_cache
+    folder, reqs, refs = setup
+    model, cfg = load_model(folder, "bfloat16", "cuda")
+    ops = model.ops
+    chosen = ops.decode_kernel, ops.prefill_attention
+    ops.decode_kernel, ops.prefill_attention = decode_kernel, prefill_kernel
+    try:
+        steps = schedules.mixed(reqs)
+        cache = make_cache(model, 16, schedules.tokens_held(steps, 64) // 16, 4)
+        runner = ModelRunner(model, cache, ops, use_graphs=True)
+        got = schedules.replay(runner, steps)
+        ops.check_status()
+    finally:
+        ops.decode_kernel, ops.prefill_attention = chosen
+    for rid, ids in reqs.items():
+        ref = refs[rid]
+        scale = float(ref.abs().max())
+        for p in range(len(ids)):
+            err = float((got[(rid, p)] - ref[p]).abs().max()) / scale
+            assert err <= BF16_BOUND_16_LAYERS, (rid, p, err)
