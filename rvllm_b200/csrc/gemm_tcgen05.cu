@@ -346,7 +346,10 @@ extern "C" int rv_gemm_tcgen05_splits(int N, int K) {
     static int pow2 = env_int("RVLLM_GEMM_POW2", 1);
     if (pow2) {        // doubling until about one block per SM, at least four stages each
         int s = 1;
-        while (s < 8 && tiles * s < 148 && kblocks / (2 * s) >= 4) s *= 2;
+        // RVLLM_GEMM_MINBLOCKS: measured in the LFM2-1.2B decode step at batch 8: 128 (gate|up
+        // unsplit) 0.973 ms, 148 0.947 ms, 222 0.985 ms, 296 1.062 ms
+        static int min_blocks = env_int("RVLLM_GEMM_MINBLOCKS", 148);
+        while (s < 8 && tiles * s < min_blocks && kblocks / (2 * s) >= 4) s *= 2;
         return s;
     }
     int best = 1;
