@@ -20,6 +20,8 @@ steps it holds 4096 - K tokens, then K steps are timed with CUDA events and end 
              values and convolution states) / its time, against the HBM peak
   points     decoded tokens a second at batch 1 and batch 64 (context 2,048 + steps)
 
+RVLLM_BENCH_PAGE sets the tokens per cache page (16; 64 measured the same).
+
 Peaks come from MEASURED_PEAKS.json beside this file when it exists ("of measured"),
 else from the fallback figures 6.65 TB/s and 1.59 PFLOP/s ("of fallback").
 """
@@ -51,7 +53,7 @@ SIZES = {
 }
 CONTEXT = 4096
 PREFILL_TOKENS = 2048
-PAGE = 16
+PAGE = int(os.environ.get("RVLLM_BENCH_PAGE", "16"))      # tokens per cache page
 
 
 def peaks():
