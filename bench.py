@@ -28,6 +28,7 @@ else from the fallback figures 6.65 TB/s and 1.59 PFLOP/s ("of fallback").
 import argparse
 import json
 import os
+import shutil
 import subprocess
 import sys
 import tempfile
@@ -154,12 +155,11 @@ def run_ours(args):
         raise SystemExit(f"--steps + --warmup must stay below {CONTEXT - 64}")
     tmp = tempfile.mkdtemp(prefix="rvllm_bench_")
     t0 = time.time()
-    folder = write_random_model(os.path.join(tmp, "lfm2_1_2b"), cfg, seed=0)
-    model, cfg = load_model(folder, "bfloat16", "cuda")
-    for f in os.listdir(folder):
-        os.remove(os.path.join(folder, f))
-    os.rmdir(folder)
-    os.rmdir(tmp)
+    try:
+        folder = write_random_model(os.path.join(tmp, "lfm2_1_2b"), cfg, seed=0)
+        model, cfg = load_model(folder, "bfloat16", "cuda")
+    finally:                     # gigabytes of weights: never leave them behind
+        shutil.rmtree(tmp, ignore_errors=True)
     setup_s = time.time() - t0
     ops = model.ops
     spec = architecture(cfg.architecture).build_spec(cfg)

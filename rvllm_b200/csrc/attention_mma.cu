@@ -552,7 +552,7 @@ paged_attention_decode_stream_kernel(
     const int* __restrict__ ctx_lens, float* __restrict__ part_o, float2* __restrict__ part_ml,
     int max_splits, int item_tiles, int num_heads, int num_kv_heads, int page_size,
     float scale_log2, int window, int n_reqs, int* __restrict__ status) {
-    rv_pdl_prologue();
+    rv_pdl_launch_dependents();     // the wait comes after the first look at the block table
     static_assert(HD == 64, "the stream kernel's stages are 128-byte rows");
     constexpr int LD = HD + 8;                                      // query rows stay padded
     constexpr int KSTEPS = HD / 16;
@@ -604,7 +604,8 @@ paged_attention_decode_stream_kernel(
         const int blk = ((split * item_keys) >> page_shift) + lane;
         if (lane < ppi && blk < max_blocks) nx_page = block_table[(size_t)r * max_blocks + blk];
     };
-    fetch_ahead((lk * W + w) * nb + b);
+    fetch_ahead((lk * W + w) * nb + b);   // index arrays of the step: not the previous kernel's
+    rv_pdl_wait();                         // keys, values and queries are the previous kernels'
     int n_loaded = 0, n_consumed = 0;
 
     // move to the next item that has keys; false when there is none

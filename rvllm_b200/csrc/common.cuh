@@ -91,8 +91,13 @@ __device__ __forceinline__ float rv_block_max(float v, float* scratch) {
 // attribute and begins with `rv_pdl_prologue()`: it lets the next kernel of the stream
 // start (and run whatever it does before its own wait, e.g. the matrix product's copies
 // of weight tiles), then waits until the previous kernel has completed and its writes
-// are visible.  Nothing is read from or written to global memory before the wait except
-// constant weights.  RVLLM_PDL=0 turns the attribute off (the two instructions are then
+// are visible.  Before the wait a kernel reads only what no kernel of the same step writes:
+// constant weights and tables and the step's index arrays (positions, slots, block tables,
+// context lengths: copied from the host before the step's first kernel); it writes nothing.
+// (Not even state that "only this layer" writes: a run order may name a layer twice, and
+// several short kernels can be resident and waiting at once.)  A few
+// kernels therefore split the prologue into `rv_pdl_launch_dependents()`, those loads, and
+// `rv_pdl_wait()`.  RVLLM_PDL=0 turns the attribute off (the two instructions are then
 // no-ops).
 __device__ __forceinline__ void rv_pdl_launch_dependents() {
     asm volatile("griddepcontrol.launch_dependents;" ::);

@@ -117,7 +117,7 @@ __global__ void qk_norm_rope_write_vec_kernel(
     float eps, const float* __restrict__ cos_table, const float* __restrict__ sin_table,
     const int* __restrict__ positions, const int* __restrict__ slot_mapping,
     T* __restrict__ k_cache, T* __restrict__ v_cache) {
-    rv_pdl_prologue();
+    rv_pdl_launch_dependents();
     const int heads_total = num_heads + 2 * num_kv_heads;
     const int half = head_dim >> 1;
     const int lph = head_dim >> 4;                       // lanes per head
@@ -133,6 +133,21 @@ __global__ void qk_norm_rope_write_vec_kernel(
     const bool is_v = live && h >= num_heads + num_kv_heads;
     const bool is_q = live && h < num_heads;
     const float* w = is_q ? q_weight : k_weight;
+    // what does not depend on the previous kernel comes before the wait for it: the slot, the
+    // norm weights and the rotation angles of this token's position
+    const int slot = (live && !is_q) ? slot_mapping[t] : 0;
+    float wa[8], wb[8], c[8], sn[8];
+    const bool normed = live && !is_v && w != nullptr, rotated = live && !is_v && cos_table != nullptr;
+    if (normed) {
+        rv_load8(w + d0, wa);
+        rv_load8(w + half + d0, wb);
+    }
+    if (rotated) {
+        const size_t trow = (size_t)positions[t] * half + d0;
+        rv_load8(cos_table + trow, c);
+        rv_load8(sin_table + trow, sn);
+    }
+    rv_pdl_wait();
     float a[8], b[8];
     float ss = 0.f;
     T* src = qkv + (size_t)t * row_stride + (size_t)(live ? h : 0) * head_dim;
@@ -145,7 +160,6 @@ __global__ void qk_norm_rope_write_vec_kernel(
     // sum over the lanes of this head (groups of lph lanes; every lane of the warp takes part)
     for (int o = lph >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
     if (!live) return;
-    const int slot = is_q ? 0 : slot_mapping[t];
     if (!is_q && slot < 0) return;
     if (is_v) {
         T* dst = v_cache + ((size_t)slot * num_kv_heads + (h - num_heads - num_kv_heads)) * head_dim;
@@ -153,22 +167,15 @@ __global__ void qk_norm_rope_write_vec_kernel(
         rv_store8(dst + half + d0, b);
         return;
     }
-    if (w) {
+    if (normed) {
         const float rms = sqrtf(ss / (float)head_dim + eps);
-        float wa[8], wb[8];
-        rv_load8(w + d0, wa);
-        rv_load8(w + half + d0, wb);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             a[i] = a[i] / rms * wa[i];
             b[i] = b[i] / rms * wb[i];
         }
     }
-    if (cos_table) {
-        float c[8], sn[8];
-        const size_t trow = (size_t)positions[t] * half + d0;
-        rv_load8(cos_table + trow, c);
-        rv_load8(sin_table + trow, sn);
+    if (rotated) {
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             const float xr = a[i] * c[i] - b[i] * sn[i], yr = a[i] * sn[i] + b[i] * c[i];

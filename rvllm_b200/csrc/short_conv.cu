@@ -151,7 +151,9 @@ __global__ void short_conv_vec4_kernel(const T* __restrict__ proj, const float* 
                                        const int* __restrict__ state_slot,
                                        const int* __restrict__ start_pos, T* __restrict__ out,
                                        int hidden, int taps) {
-    rv_pdl_prologue();
+    // index arrays, filter and biases do not depend on the previous kernel: they are requested
+    // before the wait for it
+    rv_pdl_launch_dependents();
     const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
     if (c >= hidden) return;
     const int r = blockIdx.y;
@@ -181,6 +183,7 @@ __global__ void short_conv_vec4_kernel(const T* __restrict__ proj, const float* 
         const T* p = proj + (size_t)(q0 + rel) * stride + c;
         return rv_f4_mul(rv_f4_add(rv_conv_load4(p), bb), rv_f4_add(rv_conv_load4(p + 2 * hidden), bxb));
     };
+    rv_pdl_wait();
     float4 old[RV_CONV_VEC_TAPS - 1], win[RV_CONV_VEC_TAPS - 1];
 #pragma unroll
     for (int i = 0; i < RV_CONV_VEC_TAPS - 1; ++i) {
