@@ -273,10 +273,11 @@ __global__ void paged_attention_merge_kernel(const float* __restrict__ part_o,
                                              const int* __restrict__ ctx_lens, T* __restrict__ out,
                                              int max_splits, int num_heads, int hd, int window,
                                              int split_keys) {
-    rv_pdl_prologue();
+    rv_pdl_launch_dependents();
     constexpr bool kFast = sizeof(T) == 2;
     const int r = blockIdx.y, h = blockIdx.x;
-    const int clen = ctx_lens[r];
+    const int clen = ctx_lens[r];                 // the step's index array: before the wait
+    rv_pdl_wait();
     T* o = out + ((size_t)r * num_heads + h) * hd;
     if (clen == 0) {
         for (int d = threadIdx.x; d < hd; d += blockDim.x) rv_store(o + d, 0.f);
@@ -286,15 +287,36 @@ __global__ void paged_attention_merge_kernel(const float* __restrict__ part_o,
     const int lo = window > 0 ? max(0, p - window + 1) : 0;
     const int s0 = lo / split_keys, s1 = p / split_keys;
     const size_t base = ((size_t)r * num_heads + h) * max_splits;
-    float M = -INFINITY;
-    for (int s = s0; s <= s1; ++s) M = fmaxf(M, part_ml[base + s].x);
-    float L = 0.f;
-    for (int s = s0; s <= s1; ++s) L += part_ml[base + s].y * rv_exp<kFast>(part_ml[base + s].x - M);
+    // Splits are combined in order, sixteen at a time: the loads of a group are independent, so
+    // a group costs one memory latency, not sixteen.
+    constexpr int GROUP = 16;
     for (int d = threadIdx.x; d < hd; d += blockDim.x) {
-        float O = 0.f;
-        for (int s = s0; s <= s1; ++s)
-            O += part_o[(base + s) * hd + d] * rv_exp<kFast>(part_ml[base + s].x - M);
-        rv_store(o + d, O / L);
+        float M = -INFINITY, L = 0.f, O = 0.f;
+        for (int sb = s0; sb <= s1; sb += GROUP) {
+            float2 ml[GROUP];
+            float po[GROUP];
+#pragma unroll
+            for (int i = 0; i < GROUP; ++i) {
+                const bool valid = sb + i <= s1;
+                ml[i] = valid ? part_ml[base + sb + i] : make_float2(-INFINITY, 0.f);
+                po[i] = valid ? part_o[(base + sb + i) * hd + d] : 0.f;
+            }
+            float mg = M;
+#pragma unroll
+            for (int i = 0; i < GROUP; ++i) mg = fmaxf(mg, ml[i].x);
+            if (mg == -INFINITY) continue;
+            const float keep = rv_exp<kFast>(M - mg);          // M = -inf -> 0
+            O *= keep;
+            L *= keep;
+#pragma unroll
+            for (int i = 0; i < GROUP; ++i) {
+                const float w = ml[i].y > 0.f ? rv_exp<kFast>(ml[i].x - mg) : 0.f;
+                O += po[i] * w;
+                L += ml[i].y * w;
+            }
+            M = mg;
+        }
+        rv_store(o + d, L > 0.f ? O / L : 0.f);
     }
 }
 
