@@ -57,9 +57,16 @@ __global__ void argmax_parts_kernel(const float* __restrict__ logits, float* __r
     const int per = (vocab + parts - 1) / parts;
     const int a = blockIdx.y * per, b = min(vocab, a + per);
     RvBest best = {-INFINITY, 0x7fffffff};
-    for (int i = a + threadIdx.x; i < b; i += blockDim.x) {
-        const float v = row[i];
-        if (v > best.v) { best.v = v; best.i = i; }   // false for NaN; strict keeps the earliest
+    // four loads in flight per thread (a load and its compare per iteration would cost one
+    // memory latency each); compared in index order, and strict, so the earliest maximum stays
+    const int bd = blockDim.x;
+    for (int i = a + threadIdx.x; i < b; i += 4 * bd) {
+        float v[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) v[k] = i + k * bd < b ? row[i + k * bd] : -INFINITY;
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+            if (v[k] > best.v) { best.v = v[k]; best.i = i + k * bd; }   // false for NaN
     }
     best = rv_block_best(best, sv, si);
     if (threadIdx.x == 0) {
