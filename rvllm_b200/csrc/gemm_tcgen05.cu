@@ -120,6 +120,13 @@ __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+// The same meeting without memory ordering: it only keeps every block alive until all have
+// finished reading the others' shared memory (a release here would first wait for the
+// output stores just issued).
+__device__ __forceinline__ void cluster_sync_relaxed() {
+    asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
+}
 __device__ __forceinline__ float ld_cluster_f32(const float* local, unsigned rank) {
     unsigned remote;
     float v;
@@ -290,7 +297,7 @@ __global__ void __launch_bounds__(128) gemm_tcgen05_kernel(
             rv_store(out + (size_t)t * N + n, acc);
         }
     }
-    cluster_sync_all();                                       // nobody leaves while it is read
+    cluster_sync_relaxed();                                   // nobody leaves while it is read
 }
 
 // ---- host side ----------------------------------------------------------------------------
