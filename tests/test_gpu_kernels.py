@@ -191,6 +191,8 @@ ATTN_CASES = [
     ([1, 1, 1, 2], [300, 255, 9, 130], 12, 4, 64, 8, 100),
     ([1, 1, 1], [1030, 33, 512], 4, 1, 64, 32, None),
     ([1, 1], [400, 70], 2, 2, 64, 64, 129),
+    # 32 query heads on one key/value head: two tiles of 16 packed rows per head group
+    ([1, 1, 3], [300, 70, 40], 32, 1, 64, 16, None),
 ]
 
 
@@ -365,6 +367,8 @@ PREFILL_CASES = [
     ([50, 2], [50, 700], 3, 3, 64, 64, None),
     ([300], [1000], 5, 1, 64, 16, 257),
     ([257], [257], 1, 1, 64, 16, None),
+    ([20, 9], [90, 9], 32, 1, 64, 16, None),      # 4 query tokens per block of 128 rows
+    ([15], [75], 7, 1, 64, 8, None),              # 18 tokens x 7 heads = 126 rows, 2 unused
 ]
 
 
