@@ -135,11 +135,31 @@ __device__ __forceinline__ float ld_cluster_f32(const float* local, unsigned ran
     return v;
 }
 
-template <typename TO>
+// What the q|k|v product's epilogue needs to finish the job of the q/k norm + rotation + cache
+// write kernel (head size 64: a tile of 128 weight rows is two whole heads).
+struct RvQkvEpilogue {
+    const float* q_weight;        // [64] or null
+    const float* k_weight;        // [64] or null
+    const float* cos_table;       // [positions, 32] or null (no rotation)
+    const float* sin_table;
+    const int* positions;         // [tokens]
+    const int* slot_mapping;      // [tokens]: page * page_size + offset, or -1
+    bf16* k_cache;                // [slots, kv_heads, 64]
+    bf16* v_cache;
+    float eps;
+    int num_heads, num_kv_heads;
+};
+
+// QKV = false: y = x . W^T.  QKV = true (bfloat16 output, up to 16 tokens, head size 64): W is
+// the q|k|v projection; the sums are rounded to bfloat16 as they would be stored, then each
+// query and key head is RMS-normalised and rotated, queries go to `out`, keys and values to
+// their slots of the paged cache: the separate kernel for that, and its place in the chain of
+// dependent launches, are gone.
+template <typename TO, bool QKV>
 __global__ void __launch_bounds__(128) gemm_tcgen05_kernel(
     const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
     TO* __restrict__ out, int* __restrict__ status, int M, int N, int kblocks, int n_pad,
-    int stages) {
+    int stages, const RvQkvEpilogue epi) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // the dynamic segment is aligned by hand: swizzled tiles need 1024-byte alignment
     unsigned char* base = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -271,7 +291,7 @@ __global__ void __launch_bounds__(128) gemm_tcgen05_kernel(
             const int t = c + j;
             if (t < M) {
                 const float v = good ? __uint_as_float(r[j]) : 0.f;
-                if (splits == 1) {
+                if (splits == 1 && !QKV) {
                     if (n < N && good) rv_store(out + (size_t)t * N + n, v);
                 } else {
                     park[t * RV_GEMM_BM + n_local] = v;
@@ -284,6 +304,54 @@ __global__ void __launch_bounds__(128) gemm_tcgen05_kernel(
     if (warp == 1) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
                      "r"(tmem_cols));
+    }
+    if (QKV) {
+        // ---- q|k|v: this block finishes its tokens (t = split, split + splits, ...) ------------
+        __shared__ float red[4];
+        __shared__ float xs[RV_GEMM_BM];
+        if (splits > 1) cluster_sync_all();                   // all partial tiles are parked
+        const int hcol = n >> 6, d = n & 63, lh = n_local >> 6;
+        const int kind = hcol < epi.num_heads ? 0 : (hcol < epi.num_heads + epi.num_kv_heads ? 1 : 2);
+        const float* wv = kind == 0 ? epi.q_weight : epi.k_weight;
+        const bool normed = kind < 2 && wv != nullptr && n < N;
+        const float wgt = normed ? wv[d] : 1.f;
+        for (int t = split; t < M; t += splits) {
+            float acc = 0.f;
+            for (int s = 0; s < splits; ++s)
+                acc += ld_cluster_f32(park + t * RV_GEMM_BM + n_local, (unsigned)s);
+            const float x = __bfloat162float(__float2bfloat16_rn(acc));   // as it would be stored
+            const int slot = epi.slot_mapping[t];
+            float c = 1.f, sn = 0.f;
+            if (kind < 2 && epi.cos_table && n < N) {
+                const size_t trow = (size_t)epi.positions[t] * 32 + (d & 31);
+                c = epi.cos_table[trow];
+                sn = epi.sin_table[trow];
+            }
+            const float ss_w = rv_warp_sum(x * x);
+            if (lane == 0) red[warp] = ss_w;
+            __syncthreads();
+            float xn = x;
+            if (normed) xn = x / sqrtf((red[2 * lh] + red[2 * lh + 1]) / 64.f + epi.eps) * wgt;
+            xs[n_local] = xn;
+            __syncthreads();
+            float res = xn;
+            if (kind < 2 && epi.cos_table) {
+                const float other = xs[n_local ^ 32];         // dimension d + 32 or d - 32
+                res = d < 32 ? xn * c - other * sn : other * sn + xn * c;
+            }
+            if (n < N && good) {
+                if (kind == 0) {
+                    rv_store(out + (size_t)t * N + n, res);
+                } else if (slot >= 0) {
+                    bf16* cache = kind == 1 ? epi.k_cache : epi.v_cache;
+                    const int hh = hcol - epi.num_heads - (kind == 2 ? epi.num_kv_heads : 0);
+                    cache[((size_t)slot * epi.num_kv_heads + hh) * 64 + d] = __float2bfloat16_rn(res);
+                }
+            }
+            __syncthreads();                                  // red and xs are used again
+        }
+        if (splits > 1) cluster_sync_relaxed();               // nobody leaves while it is read
+        return;
     }
     if (splits == 1) return;
 
@@ -387,21 +455,24 @@ static int pick_stages(int n_pad) {
 // Once per process, outside any stream capture: raise the kernels' shared-memory limit and
 // look up the driver's tensor-map encoder.
 extern "C" int rv_gemm_tcgen05_init() {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<bf16>,
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<bf16, false>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          RV_GEMM_SMEM_LIMIT);
     if (e == cudaSuccess)
-        e = cudaFuncSetAttribute(gemm_tcgen05_kernel<float>,
+        e = cudaFuncSetAttribute(gemm_tcgen05_kernel<float, false>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, RV_GEMM_SMEM_LIMIT);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(gemm_tcgen05_kernel<bf16, true>,
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, RV_GEMM_SMEM_LIMIT);
     if (e != cudaSuccess) RV_FAIL("gemm_tcgen05: %s", cudaGetErrorString(e));
     if (!encode_fn()) RV_FAIL("gemm_tcgen05: cuTensorMapEncodeTiled is not available in this driver");
     return 0;
 }
 
-template <typename TO>
+template <typename TO, bool QKV>
 static int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, void* out, int* status, int M,
                   int N, int kblocks, int n_pad, int stages, int tiles, int splits, size_t smem,
-                  cudaStream_t stream) {
+                  const RvQkvEpilogue& epi, cudaStream_t stream) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(tiles, splits, 1);
     cfg.blockDim = dim3(128, 1, 1);
@@ -416,8 +487,8 @@ static int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, void* out,
     attr[1].val.programmaticStreamSerializationAllowed = rv_pdl_enabled();
     cfg.attrs = attr;
     cfg.numAttrs = 2;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<TO>, map_w, map_x, (TO*)out, status,
-                                       M, N, kblocks, n_pad, stages);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<TO, QKV>, map_w, map_x, (TO*)out,
+                                       status, M, N, kblocks, n_pad, stages, epi);
     if (e != cudaSuccess) RV_FAIL("gemm_tcgen05: %s", cudaGetErrorString(e));
     return 0;
 }
@@ -425,8 +496,8 @@ static int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, void* out,
 // y = x . W^T.  `status` is a device int the kernel sets to a non-zero code if a bounded
 // wait ran out (1: producer waiting for a free stage, 2: copies still in flight at exit,
 // 3: MMA issuer waiting for data, 4: epilogue waiting for the accumulator).
-extern "C" int rv_gemm_tcgen05(const void* x, const void* w, void* out, int out_dtype, int* status,
-                               int M, int N, int K, void* stream) {
+static int gemm(const void* x, const void* w, void* out, int out_dtype, int* status, int M, int N,
+                int K, const RvQkvEpilogue* epi, void* stream) {
     if (M == 0) return 0;
     if (M < 0 || M > 256 || N <= 0 || K <= 0)
         RV_FAIL("gemm_tcgen05: sizes out of range (M = %d must be 1..256, N = %d, K = %d)", M, N, K);
@@ -446,9 +517,52 @@ extern "C" int rv_gemm_tcgen05(const void* x, const void* w, void* out, int out_
     if (make_map(&map_x, x, M, K, n_pad)) return 1;
     const size_t smem = ring + 1024;
     cudaStream_t s = (cudaStream_t)stream;
+    const RvQkvEpilogue none = {};
+    if (epi) {
+        if (out_dtype != RV_DTYPE_BF16 || M > 16)
+            RV_FAIL("gemm_tcgen05: the q|k|v epilogue takes bfloat16 and up to 16 tokens");
+        return launch<bf16, true>(map_w, map_x, out, status, M, N, kblocks, n_pad, stages, tiles, splits,
+                                  smem, *epi, s);
+    }
     if (out_dtype == RV_DTYPE_BF16)
-        return launch<bf16>(map_w, map_x, out, status, M, N, kblocks, n_pad, stages, tiles, splits, smem, s);
+        return launch<bf16, false>(map_w, map_x, out, status, M, N, kblocks, n_pad, stages, tiles, splits,
+                                   smem, none, s);
     if (out_dtype == RV_DTYPE_F32)
-        return launch<float>(map_w, map_x, out, status, M, N, kblocks, n_pad, stages, tiles, splits, smem, s);
+        return launch<float, false>(map_w, map_x, out, status, M, N, kblocks, n_pad, stages, tiles,
+                                    splits, smem, none, s);
     RV_FAIL("gemm_tcgen05: unknown output dtype code %d", out_dtype);
+}
+
+extern "C" int rv_gemm_tcgen05(const void* x, const void* w, void* out, int out_dtype, int* status,
+                               int M, int N, int K, void* stream) {
+    return gemm(x, w, out, out_dtype, status, M, N, K, nullptr, stream);
+}
+
+// out[M, N] gets the normalised, rotated queries (its key and value columns are not written);
+// keys and values go to `k_cache` / `v_cache` at `slot_mapping`.  Head size 64, bfloat16,
+// M <= 16, N = (num_heads + 2 num_kv_heads) * 64.  Null weights: no norm; null tables: no
+// rotation.
+extern "C" int rv_gemm_tcgen05_qkv(const void* x, const void* w, void* out, int* status, int M,
+                                   int N, int K, int num_heads, int num_kv_heads,
+                                   const float* q_weight, const float* k_weight, float eps,
+                                   const float* cos_table, const float* sin_table,
+                                   const int* positions, const int* slot_mapping, void* k_cache,
+                                   void* v_cache, void* stream) {
+    if (N != (num_heads + 2 * num_kv_heads) * 64)
+        RV_FAIL("gemm_tcgen05_qkv: N = %d is not (heads + 2 kv heads) * 64", N);
+    if (!slot_mapping || !k_cache || !v_cache || (cos_table && (!sin_table || !positions)))
+        RV_FAIL("gemm_tcgen05_qkv: incomplete cache or rotation arguments");
+    RvQkvEpilogue epi;
+    epi.q_weight = q_weight;
+    epi.k_weight = k_weight;
+    epi.cos_table = cos_table;
+    epi.sin_table = sin_table;
+    epi.positions = positions;
+    epi.slot_mapping = slot_mapping;
+    epi.k_cache = (bf16*)k_cache;
+    epi.v_cache = (bf16*)v_cache;
+    epi.eps = eps;
+    epi.num_heads = num_heads;
+    epi.num_kv_heads = num_kv_heads;
+    return gemm(x, w, out, RV_DTYPE_BF16, status, M, N, K, &epi, stream);
 }

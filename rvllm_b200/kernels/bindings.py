@@ -74,6 +74,9 @@ class CudaOps:
         self.gemm_small_m = int(os.environ.get("RVLLM_GEMM_SMALL_M", "16"))
         self.gemm_mode = os.environ.get("RVLLM_GEMM", "tcgen05")
         self._gemm_state = {}
+        # q/k norm + rotation + cache write inside the q|k|v product's epilogue (few bfloat16
+        # tokens, head size 64); "0": always the separate kernel
+        self.fuse_qkv_rope = os.environ.get("RVLLM_FUSE_QKV_ROPE", "1") == "1"
         self._check(self.lib.rv_gemm_tcgen05_init(), "gemm_tcgen05 set-up")
         # float32 products must be float32: no TF32, no reduced-precision accumulation
         torch.backends.cuda.matmul.allow_tf32 = False
@@ -173,6 +176,34 @@ class CudaOps:
                 and out_dtype in (torch.bfloat16, torch.float32)
                 and (self.gemm_mode == "tcgen05"
                      or (w.shape[0] <= 18 * 128 and x.shape[1] >= 4096)))
+
+    def linear_qk_norm_rope_write(self, x, w_qkv, num_heads, num_kv_heads, head_dim, q_weight,
+                                  k_weight, eps, table, positions, slot_mapping, k_cache, v_cache,
+                                  out_dtype=None):
+        """q|k|v = x . w_qkv^T, then per-head q/k norm, rotation and the cache write; returns
+        the [tokens, (heads + 2 kv heads) * head_dim] buffer whose query columns attention
+        reads.  Few bfloat16 tokens with head size 64 and a cache to write: one kernel (the
+        product's epilogue does the rest); otherwise the product and `qk_norm_rope_write`."""
+        out_dtype = out_dtype or x.dtype
+        if (self.fuse_qkv_rope and k_cache is not None and num_kv_heads > 0 and head_dim == 64
+                and out_dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16
+                and w_qkv.shape[0] == (num_heads + 2 * num_kv_heads) * 64
+                and self._small_product(x, w_qkv, out_dtype)):
+            m, k = x.shape
+            n = w_qkv.shape[0]
+            qkv = torch.empty((m, n), dtype=out_dtype, device=x.device)
+            cos, sin = table if table is not None else (None, None)
+            self._check(self.lib.rv_gemm_tcgen05_qkv(
+                _ptr(x), _ptr(w_qkv), _ptr(qkv), _ptr(self._gemm_status(x.device)), c_int(m),
+                c_int(n), c_int(k), c_int(num_heads), c_int(num_kv_heads), _ptr(q_weight),
+                _ptr(k_weight), c_float(eps), _ptr(cos), _ptr(sin), _ptr(positions),
+                _ptr(slot_mapping), _ptr(k_cache), _ptr(v_cache), self._stream()),
+                "gemm_tcgen05_qkv")
+            return qkv
+        qkv = self.linear(x, w_qkv, out_dtype=out_dtype)
+        self.qk_norm_rope_write(qkv, num_heads, num_kv_heads, head_dim, q_weight, k_weight, eps,
+                                table, positions, slot_mapping, k_cache, v_cache)
+        return qkv
 
     def linear(self, x, w, bias=None, out_dtype=None):
         out_dtype = out_dtype or x.dtype

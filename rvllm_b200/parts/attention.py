@@ -7,7 +7,8 @@ k^T / sqrt(head_dim)) v over the keys at or before the query's position, query h
 [g*G, (g+1)*G) sharing key/value head g (src/model.rs:377-415); output projection.
 
 What differs by design: q, k and v are one [(heads + 2 kv_heads) * head_dim, hidden]
-matrix product; norm, rotation and the cache write are one kernel; attention reads
+matrix product; norm, rotation and the cache write are one kernel (for a few tokens: the
+product's own epilogue); attention reads
 the pages through the block table instead of gathering them into a dense batch
 (src/kv_storage.rs:157-173), keeps no score matrix and needs no mask tensor
 (src/model.rs:347-372): a key at position j is visible to a query at position p iff
@@ -83,13 +84,13 @@ class Attention(Mixer):
         if owns and not self.has_kv:
             raise ValueError("attention: this call owns a cache but the block has no "
                              "key and value projections")
-        qkv = self.ops.linear(normed, self.w_qkv if owns else self.w_q, out_dtype=self.dtype)
         group = ctx.groups[cache.group]
-        self.ops.qk_norm_rope_write(
-            qkv, s.num_heads, s.num_kv_heads if owns else 0, s.head_dim,
+        qkv = self.ops.linear_qk_norm_rope_write(
+            normed, self.w_qkv if owns else self.w_q, s.num_heads,
+            s.num_kv_heads if owns else 0, s.head_dim,
             self.q_norm, self.k_norm if owns else None, s.qk_norm.eps if s.qk_norm else 0.0,
             self.position.rotation_table(), ctx.positions, group.slot_mapping,
-            cache.k if owns else None, cache.v if owns else None)
+            cache.k if owns else None, cache.v if owns else None, out_dtype=self.dtype)
         out = torch.empty((normed.shape[0], s.num_heads * s.head_dim), dtype=self.dtype,
                           device=normed.device)
         self.ops.paged_attention(qkv, s.num_heads, s.num_kv_heads, s.head_dim,

@@ -48,6 +48,14 @@ class PlainOps:
             y = y + _f(bias)
         return y.to(out_dtype or x.dtype)
 
+    def linear_qk_norm_rope_write(self, x, w_qkv, num_heads, num_kv_heads, head_dim, q_weight,
+                                  k_weight, eps, table, positions, slot_mapping, k_cache, v_cache,
+                                  out_dtype=None):
+        qkv = self.linear(x, w_qkv, out_dtype=out_dtype or x.dtype)
+        self.qk_norm_rope_write(qkv, num_heads, num_kv_heads, head_dim, q_weight, k_weight, eps,
+                                table, positions, slot_mapping, k_cache, v_cache)
+        return qkv
+
     def add_bias(self, x, bias):
         x.copy_((_f(x) + _f(bias)).to(x.dtype))
 

@@ -130,6 +130,66 @@ def test_qk_norm_rope_write(ops, dtype, norm, rope):
     assert torch.equal(d_v.cpu(), ref_v)
 
 
+@pytest.mark.parametrize("norm,rope", [(True, True), (False, True), (True, False)])
+@pytest.mark.parametrize("sizes", [
+    # tokens, heads, kv heads, hidden: an odd number of heads in all (the last tile of 128 rows
+    # holds one head), K split over a cluster and not, one token and the most the kernel takes
+    (8, 6, 2, 512), (1, 3, 1, 72), (16, 5, 2, 4096), (11, 32, 8, 2048),
+])
+def test_linear_qk_norm_rope_write(ops, sizes, norm, rope):
+    """The q|k|v product with norm, rotation and cache write in its epilogue (bfloat16, head
+    size 64, few tokens) against the product followed by the plain norm/rotation/write."""
+    n, nh, nkv, hidden = sizes
+    hd, ps, pages = 64, 8, 9
+    g = torch.Generator().manual_seed(14)
+    x = rnd((n, hidden), torch.bfloat16, g)
+    w = rnd(((nh + 2 * nkv) * hd, hidden), torch.bfloat16, g, 0.05)
+    qw = (1 + rnd((hd,), torch.float32, g, 0.1)) if norm else None
+    kw = (1 + rnd((hd,), torch.float32, g, 0.1)) if norm else None
+    positions = torch.randint(0, 300, (n,), generator=g, dtype=torch.int32)
+    table = None
+    if rope:
+        ang = torch.arange(300).float().unsqueeze(1) * torch.pow(
+            torch.tensor(10000.0), -2.0 * torch.arange(hd // 2).float() / hd)
+        table = (ang.cos(), ang.sin())
+    slots = torch.randperm(pages * ps, generator=g)[:n].to(torch.int32)
+    if n > 5:
+        slots[5] = -1
+    kc = rnd((pages, ps, nkv, hd), torch.bfloat16, g)
+    vc = rnd((pages, ps, nkv, hd), torch.bfloat16, g)
+    ref_k, ref_v = kc.clone(), vc.clone()
+    ref_qkv = PlainOps().linear_qk_norm_rope_write(x, w, nh, nkv, hd, qw, kw, 1e-6, table,
+                                                  positions, slots, ref_k, ref_v)
+    dev = lambda t: None if t is None else t.cuda()
+    results = []
+    fused = ops.fuse_qkv_rope
+    try:
+        for mode in (True, False):
+            ops.fuse_qkv_rope = mode
+            d_k, d_v = kc.cuda(), vc.cuda()
+            d_qkv = ops.linear_qk_norm_rope_write(
+                x.cuda(), w.cuda(), nh, nkv, hd, dev(qw), dev(kw), 1e-6,
+                (table[0].cuda(), table[1].cuda()) if rope else None, positions.cuda(),
+                slots.cuda(), d_k, d_v)
+            ops.check_status()
+            results.append((d_qkv[:, :nh * hd].cpu().float(), d_k.cpu().float(), d_v.cpu().float()))
+    finally:
+        ops.fuse_qkv_rope = fused
+    scale = float(ref_qkv.float().abs().max())
+    for q_out, k_out, v_out in results:
+        # the product's rounding to bfloat16 sits before the norm: a last-bit difference of
+        # the product is a last-bit difference of the result
+        assert (q_out - ref_qkv[:, :nh * hd].float()).abs().max() <= 2e-2 * scale
+        assert (k_out - ref_k.float()).abs().max() <= 2e-2 * scale
+        assert (v_out - ref_v.float()).abs().max() <= 2e-2 * scale
+    # the slot -1 row wrote nothing; untouched slots are untouched
+    written = set(int(s_) for s_ in slots.tolist() if s_ >= 0)
+    flat_k = results[0][1].reshape(pages * ps, -1)
+    for slot in range(pages * ps):
+        if slot not in written:
+            assert torch.equal(flat_k[slot], kc.float().reshape(pages * ps, -1)[slot])
+
+
 def attention_case(dtype, g, q_lens, ctx_lens, nh, nkv, hd, ps, window=None, standout=False):
     """A batch with random pages in a shuffled pool.  With `standout`, one far key of
     every request is made to dominate the softmax of its last query."""
