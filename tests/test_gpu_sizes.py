@@ -95,3 +95,32 @@ def test_real_sizes_each_attention_kernel(setup, decode_kernel, prefill_kernel):
         for p in range(len(ids)):
             err = float((got[(rid, p)] - ref[p]).abs().max()) / scale
             assert err <= BF16_BOUND_16_LAYERS, (rid, p, err)
+
+
+def test_decode_step_fuses_qk_rope_into_the_product(setup):
+    """A decode step at these sizes (head size 64, bfloat16) runs the q/k norm + rotation +
+    cache write inside the q|k|v product: one launch less per attention layer than with the
+    separate kernel, and the same logits within bfloat16 rounding."""
+    from rvllm_b200.engine import ModelRunner, StepEntry, load_model, make_cache
+    folder, reqs, refs = setup
+    model, cfg = load_model(folder, "bfloat16", "cuda")
+    ops = model.ops
+    ids = reqs["s1"]
+    fused = ops.fuse_qkv_rope
+    out, launches = {}, {}
+    try:
+        for mode in (True, False):
+            ops.fuse_qkv_rope = mode
+            cache = make_cache(model, 16, 8, 1)
+            runner = ModelRunner(model, cache, ops, use_graphs=False)
+            runner.add_request("r")
+            runner.step([StepEntry("r", ids[:-1], ())])
+            before = ops.launches
+            out[mode] = runner.step([StepEntry("r", ids[-1:], (0,))])[0].float().cpu()
+            launches[mode] = ops.launches - before
+    finally:
+        ops.fuse_qkv_rope = fused
+    ops.check_status()
+    assert launches[False] - launches[True] == len(LFM2_350M["full_attn_idxs"])
+    scale = float(out[False].abs().max())
+    assert float((out[True] - out[False]).abs().max()) <= BF16_BOUND_16_LAYERS * scale
