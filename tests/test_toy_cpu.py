@@ -32,6 +32,7 @@ def test_toy_is_built_from_registered_parts(setup):
     kinds = [type(b.mixer).__name__ for b in model.blocks]
     assert kinds == ["ToyDecay", "Attention", "Attention", "ToyDecay"]
     assert type(model.blocks[0].feed_forward).__name__ == "ScaledRelu"
+    assert type(model.blocks[3].feed_forward).__name__ == "SoftRouted"
     needs = model.cache_needs()
     assert needs[5] is None and needs[2] is not None          # the last call owns no cache
     cache = make_cache(model, 4, 64, 4)

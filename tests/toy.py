@@ -4,9 +4,13 @@ architectures plug in without touching the package:
 * `ToyDecay`, a mixer with a state of its own (one float32 vector per request):
   s_t = decay * s_{t-1} + W x_t, out_t = s_t;
 * `ScaledRelu`, another feed-forward: down(relu(up(x)) * gain);
+* `SoftRouted`, a feed-forward with a router: float32 router logits, softmax gates over
+  its experts, out = sum_e gate_e * down_e(relu(up_e(x))) (every expert weighted, so the
+  result is continuous in the logits and a test cannot flip on a near-tie);
 * `HalfRope`, another position encoding: the reference rotation at half the angle;
 * "ToyForCausalLM": blocks [decay, windowed attention with HalfRope, attention without
-  position encoding or q/k norm and a custom scale, decay], run in the order
+  position encoding or q/k norm and a custom scale, decay with the routed feed-forward],
+  run in the order
   0, 1, 2, 1(reading nothing: a second call with its own cache), 3, 2(reading the cache
   of the first call of block 2), so a block runs twice and a call reads another call's
   cache.
@@ -86,6 +90,37 @@ class ScaledRelu(FeedForward):
         return self.ops.linear(h.to(self.dtype), self.down, out_dtype=self.dtype)
 
 
+@dataclass(frozen=True)
+class SoftRoutedSpec(FeedForwardSpec):
+    width: int = 0
+    experts: int = 2
+
+
+class SoftRouted(FeedForward):
+    @staticmethod
+    def params(spec):
+        p = {"router.weight": ParamDecl((spec.experts, spec.hidden), "linear")}
+        for e in range(spec.experts):
+            p[f"experts.{e}.up.weight"] = ParamDecl((spec.width, spec.hidden), "linear")
+            p[f"experts.{e}.down.weight"] = ParamDecl((spec.hidden, spec.width), "linear")
+        return p
+
+    def __init__(self, spec, tensors, ops, dtype):
+        self.spec, self.ops, self.dtype = spec, ops, dtype
+        self.router = tensors["router.weight"]
+        self.up = [tensors[f"experts.{e}.up.weight"] for e in range(spec.experts)]
+        self.down = [tensors[f"experts.{e}.down.weight"] for e in range(spec.experts)]
+
+    def forward(self, normed, ctx):
+        gates = torch.softmax(self.ops.linear(normed, self.router, out_dtype=torch.float32), dim=-1)
+        out = torch.zeros((normed.shape[0], self.spec.hidden), dtype=torch.float32,
+                          device=normed.device)
+        for e in range(self.spec.experts):
+            h = torch.relu(self.ops.linear(normed, self.up[e], out_dtype=self.dtype))
+            out += gates[:, e:e + 1] * self.ops.linear(h, self.down[e], out_dtype=torch.float32)
+        return out.to(self.dtype)
+
+
 class HalfRope(PositionEncoding):
     def __init__(self, spec, device):
         half = spec.head_dim // 2
@@ -147,11 +182,12 @@ def toy_spec(cfg: ToyConfig) -> ModelSpec:
     plain = AttentionSpec("attention", cfg.hidden, num_heads=cfg.heads, num_kv_heads=cfg.kv_heads,
                           head_dim=cfg.head_dim, qk_norm=None, position=PositionSpec("none"),
                           window=None, scale=0.3)
+    routed = SoftRoutedSpec("toy_soft_routed", cfg.hidden, width=cfg.width // 2, experts=3)
     layers = []
     for i, mixer in enumerate([decay, local, plain, decay]):
         p = f"blocks.{i}."
-        layers.append(BlockSpec("pre_norm", mixer, ffn, norm, norm, p + "mixer.", p + "ffn.",
-                                p + "norm1.weight", p + "norm2.weight"))
+        layers.append(BlockSpec("pre_norm", mixer, routed if i == 3 else ffn, norm, norm,
+                                p + "mixer.", p + "ffn.", p + "norm1.weight", p + "norm2.weight"))
     return ModelSpec(architecture=cfg.architecture, vocab_size=cfg.vocab_size, hidden=cfg.hidden,
                      max_position=cfg.max_position, layers=tuple(layers),
                      order=tuple(LayerCall(b, c) for b, c in ORDER), final_norm=norm,
@@ -162,6 +198,7 @@ def toy_spec(cfg: ToyConfig) -> ModelSpec:
 def register_toy():
     register_mixer("toy_decay", ToyDecay, replace=True)
     register_feed_forward("toy_scaled_relu", ScaledRelu, replace=True)
+    register_feed_forward("toy_soft_routed", SoftRouted, replace=True)
     register_position("toy_half_rope", HalfRope, replace=True)
     register_architecture("ToyForCausalLM", ToyConfig, toy_spec, replace=True)
 
@@ -176,6 +213,14 @@ def toy_plain_logits(ids, w: Dict[str, torch.Tensor], cfg: dict) -> torch.Tensor
     kv_of_call = {}
 
     def ffn(h, p):
+        if p + "router.weight" in w:
+            gates = torch.softmax(P.linear(h, w[p + "router.weight"]), dim=-1)
+            out = torch.zeros(h.shape[0], H)
+            for e in range(gates.shape[1]):
+                q = p + f"experts.{e}."
+                out = out + gates[:, e:e + 1] * P.linear(torch.relu(P.linear(h, w[q + "up.weight"])),
+                                                         w[q + "down.weight"])
+            return out
         return P.linear(torch.relu(P.linear(h, w[p + "up.weight"])) * 1.25, w[p + "down.weight"])
 
     for call, (b, cache_of) in enumerate(ORDER):
