@@ -77,12 +77,23 @@ class ClockSampler:
         self.proc = None
         self.path = None
 
+    @staticmethod
+    def _device_id() -> str:
+        """What nvidia-smi calls the device CUDA runs on: its UUID when torch can tell it
+        (CUDA_VISIBLE_DEVICES may renumber the devices), else index 0."""
+        try:
+            import torch
+            uuid = str(torch.cuda.get_device_properties(torch.cuda.current_device()).uuid)
+            return uuid if uuid.startswith("GPU-") else "GPU-" + uuid
+        except Exception:
+            return "0"
+
     def start(self):
         try:
             fd, self.path = tempfile.mkstemp(suffix=".csv")
             os.close(fd)
             self.proc = subprocess.Popen(
-                ["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}",
+                ["nvidia-smi", "-i", self._device_id(), f"--query-gpu={self.FIELDS}",
                  "--format=csv,noheader,nounits", "-lms", "100"],
                 stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
         except OSError:

@@ -34,7 +34,10 @@
 //   k_cache,     [pages, page_size, num_kv_heads, head_dim], same dtype
 //   v_cache
 //   block_table  int32 [n_reqs, max_blocks], page ids of each request
-//   ctx_lens     int32 [n_reqs], tokens in the cache including the current one; 0 skips
+//   ctx_lens     int32 [n_reqs], tokens in the cache including the current one; 0 skips.
+//                Every entry must be <= max_ctx_len: the launch covers max_ctx_len keys, and
+//                a request that claims more gets NaN in its output rows instead of a result
+//                that silently leaves keys out.
 //   out          [n_reqs, num_heads * head_dim], same dtype
 //   window       0 for none, else only the last `window` keys are visible
 // Returns 0, or non-zero with the reason in rv_last_error().

@@ -285,7 +285,13 @@ __global__ void paged_attention_merge_kernel(const float* __restrict__ part_o,
     }
     const int p = clen - 1;
     const int lo = window > 0 ? max(0, p - window + 1) : 0;
-    const int s0 = lo / split_keys, s1 = p / split_keys;
+    // A context longer than the launch's max_ctx_len has keys that no split covered: the row
+    // is marked invalid (NaN) and nothing outside this head's slots is read.
+    if (clen > max_splits * split_keys) {
+        for (int d = threadIdx.x; d < hd; d += blockDim.x) rv_store(o + d, NAN);
+        return;
+    }
+    const int s0 = lo / split_keys, s1 = min(p / split_keys, max_splits - 1);
     const size_t base = ((size_t)r * num_heads + h) * max_splits;
     // Splits are combined in order, sixteen at a time: the loads of a group are independent, so
     // a group costs one memory latency, not sixteen.

@@ -107,6 +107,19 @@ __device__ __forceinline__ void rv_pdl_prologue() {
     rv_pdl_launch_dependents();
     rv_pdl_wait();
 }
+// Streaming multiprocessors of the current device (asked once per device).
+static inline int rv_sm_count() {
+    static int cached[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+    if (cached[dev] <= 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+            n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
 static inline int rv_pdl_enabled() {
     static int v = -1;
     if (v < 0) {

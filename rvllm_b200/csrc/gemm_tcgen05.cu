@@ -416,14 +416,14 @@ extern "C" int rv_gemm_tcgen05_splits(int N, int K) {
     const int kblocks = (K + RV_GEMM_BK - 1) / RV_GEMM_BK;
     static int forced = env_int("RVLLM_GEMM_SPLITS", 0);
     static int fixed_cost = env_int("RVLLM_GEMM_FIXED", 6);
-    static int sms = env_int("RVLLM_GEMM_SLOTS", 444);
+    static int sms = env_int("RVLLM_GEMM_SLOTS", 3 * rv_sm_count());
     if (forced > 0) return forced > 8 ? 8 : (kblocks / forced < 1 ? 1 : forced);
     static int pow2 = env_int("RVLLM_GEMM_POW2", 1);
     if (pow2) {        // doubling until about one block per SM, at least four stages each
         int s = 1;
         // RVLLM_GEMM_MINBLOCKS: measured in the LFM2-1.2B decode step at batch 8: 128 (gate|up
-        // unsplit) 0.973 ms, 148 0.947 ms, 222 0.985 ms, 296 1.062 ms
-        static int min_blocks = env_int("RVLLM_GEMM_MINBLOCKS", 148);
+        // unsplit) 0.973 ms, 148 (one block per SM, the default) 0.947 ms, 222 0.985 ms, 296 1.062 ms
+        static int min_blocks = env_int("RVLLM_GEMM_MINBLOCKS", rv_sm_count());
         while (s < 8 && tiles * s < min_blocks && kblocks / (2 * s) >= 4) s *= 2;
         return s;
     }

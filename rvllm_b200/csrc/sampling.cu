@@ -99,7 +99,8 @@ __global__ void argmax_final_kernel(const float* __restrict__ part_v, const int*
 // given by rv_argmax_parts.
 extern "C" int rv_argmax_parts(int n_rows, int vocab) {
     int parts = 1;
-    while (parts < RV_ARGMAX_MAX_PARTS && n_rows * parts < 296 && vocab / (parts * 2) >= 1024) parts *= 2;
+    const int want = 2 * rv_sm_count();        // two blocks per SM
+    while (parts < RV_ARGMAX_MAX_PARTS && n_rows * parts < want && vocab / (parts * 2) >= 1024) parts *= 2;
     return parts;
 }
 

@@ -46,13 +46,19 @@ class _InFlight:
     host: object                    # pinned host copy of `ids` (or None)
     ready: object                   # event recorded after the copy (or None)
 
+    check: object = None            # called with the kernels' status word read beside the ids
+
     def tokens(self) -> List[int]:
         if self.ids is None:
             return []
         if self.ready is None:
             return self.ids.tolist()
         self.ready.synchronize()
-        return self.host.tolist()
+        got = self.host.tolist()
+        if self.check is not None:
+            # the last word is the kernels' status: a wait that ran out left invalid logits
+            self.check(got.pop())
+        return got
 
 
 class Engine:
@@ -99,16 +105,27 @@ class Engine:
             return _InFlight(plan, None, None, None)
         params = [s.request.sampling for s in who]
         counters = [len(s.generated) + extra_drawn for s in who]
+        status = getattr(self.runner.ops, "status_word", None)
         if not self.lookahead:
             ids = self.sampler.sample(logits, params, counters)
+            if status is not None:
+                self.runner.ops.check_status()
             return _InFlight(plan, _HostIds(ids), None, None)
         import torch
         ids = self.sampler.sample_device(logits, params, counters)
-        host = torch.empty(ids.shape, dtype=ids.dtype, pin_memory=True)
-        host.copy_(ids, non_blocking=True)
+        n = ids.shape[0]
+        host = torch.empty(n + (status is not None), dtype=ids.dtype, pin_memory=True)
+        host[:n].copy_(ids, non_blocking=True)
+        check = None
+        if status is not None:
+            # the kernels' status word travels with the ids: no extra synchronisation
+            word = status(ids.device)
+            host[n:].copy_(word, non_blocking=True)
+            ops = self.runner.ops
+            check = lambda code: ops.raise_for_status(code, ids.device)
         ready = torch.cuda.Event()
         ready.record()
-        return _InFlight(plan, ids, host, ready)
+        return _InFlight(plan, ids, host, ready, check)
 
     def _can_look_ahead(self, plan) -> bool:
         sch = self.scheduler
@@ -180,7 +197,7 @@ class _Subset(_InFlight):
         import torch
         rows = torch.tensor(keep, dtype=torch.long, device=base.ids.device)
         super().__init__([base.plan[i] for i in keep], base.ids.index_select(0, rows), base.host,
-                         base.ready)
+                         base.ready, None)
         self._base, self._keep = base, keep
 
     def tokens(self) -> List[int]:

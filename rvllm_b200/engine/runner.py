@@ -40,6 +40,27 @@ class ModelRunner:
         self.steps = 0
         self.graph_steps = 0
         self.capture_failures = 0
+        self._reserve_workspace()
+
+    def _reserve_workspace(self) -> None:
+        """Size the kernels' shared scratch for the largest step this cache allows (padded
+        as replayed steps pad: request count and block-table width to powers of two), so
+        that it never has to be replaced while a captured launch sequence names it."""
+        reserve = getattr(self.ops, "reserve_scratch", None)
+        if reserve is None or not self.is_cuda:
+            return
+        from ..parts.base import mixer_class
+        cache, spec = self.cache, self.model.spec
+        ps = cache.page_size
+        tokens = min(spec.max_position, max(1, cache.num_pages) * ps)
+        blocks = -(-tokens // ps)
+        context = max(16, 1 << (blocks - 1).bit_length()) * ps
+        requests = 1 << (max(1, cache.max_requests) - 1).bit_length()
+        need = 0
+        for call in spec.order:
+            m = spec.layers[call.layer].mixer
+            need = max(need, mixer_class(m.kind).workspace_bytes(m, self.ops, requests, context))
+        reserve(need, self.device)
 
     # ---- requests ----------------------------------------------------------------
 

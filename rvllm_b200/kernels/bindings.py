@@ -50,6 +50,7 @@ class CudaOps:
         self.lib.rv_last_error.restype = ctypes.c_char_p
         self.lib.rv_paged_attention_decode_scratch_bytes.restype = c_longlong
         self._scratch = {}
+        self._retired = []
         self._attn_libs = {}
         self._verbose_build = verbose_build
         # bfloat16 attention: "mma" = mma.sync tensor-core kernels (attention_mma.cu, head
@@ -139,6 +140,9 @@ class CudaOps:
     # ---- matrix product (library) -------------------------------------------------------
 
     def _gemm_status(self, device):
+        device = torch.device(device)
+        if device.index is None:
+            device = torch.device("cuda", torch.cuda.current_device())
         st = self._gemm_state.get(device)
         if st is None:
             st = torch.zeros(1, dtype=torch.int32, device=device)
@@ -156,6 +160,20 @@ class CudaOps:
             _ptr(x), _ptr(w), _ptr(y), _code(out_dtype), _ptr(self._gemm_status(x.device)),
             c_int(m), c_int(n), c_int(k), self._stream()), "gemm_tcgen05")
         return y
+
+    def status_word(self, device) -> torch.Tensor:
+        """The int32 word in which kernels on `device` record a wait that ran out (0: none).
+        A caller that already copies a step's result to the host can copy this word along
+        and pass what it read to `raise_for_status`, which costs no synchronisation."""
+        return self._gemm_status(device)
+
+    def raise_for_status(self, code: int, device=None) -> None:
+        if code != 0:
+            if device is not None:
+                self._gemm_status(device).zero_()
+            raise KernelError(f"a kernel gave up waiting on an mbarrier (code {code}: 1-4 "
+                              f"gemm_tcgen05, 12 decode attention, 21 prefill attention); its "
+                              f"output is not valid")
 
     def check_status(self) -> None:
         """Raise if a kernel recorded that one of its bounded waits ran out (this
@@ -252,11 +270,34 @@ class CudaOps:
     # ---- attention -------------------------------------------------------------------
 
     def _scratch_buffer(self, nbytes: int, device) -> torch.Tensor:
-        buf = self._scratch.get(device)
+        """The split-KV scratch of `device`, at least `nbytes` long.  A captured launch
+        sequence holds the raw address of the buffer it was captured with, so a buffer
+        that is outgrown is never given back: it moves to `_retired` and stays valid for
+        every graph that names it.  Growth doubles, so the retired ones together are
+        smaller than the live one."""
+        key = str(device)
+        buf = self._scratch.get(key)
         if buf is None or buf.numel() < nbytes:
-            buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
-            self._scratch[device] = buf
+            size = max(nbytes, 1 << 20, 2 * buf.numel() if buf is not None else 0)
+            if buf is not None:
+                self._retired.append(buf)
+            buf = torch.empty(size, dtype=torch.uint8, device=device)
+            self._scratch[key] = buf
         return buf
+
+    def attention_scratch_bytes(self, n_reqs: int, num_heads: int, head_dim: int,
+                                max_ctx_len: int) -> int:
+        """Bytes of split-KV scratch the decode attention kernels need at most for
+        `n_reqs` single-token requests of up to `max_ctx_len` cached tokens (with the
+        smallest split any of them uses, 128 keys)."""
+        return int(self.lib.rv_paged_attention_decode_scratch_bytes(
+            c_int(n_reqs), c_int(num_heads), c_int(head_dim), c_int(2 * max_ctx_len)))
+
+    def reserve_scratch(self, nbytes: int, device) -> None:
+        """Size the scratch before any launch sequence is captured, so that it does not
+        have to grow afterwards."""
+        if nbytes > 0:
+            self._scratch_buffer(nbytes, device)
 
     def _attn_lib(self, head_dim: int):
         """The tensor-core attention library for this head size, built at first use."""

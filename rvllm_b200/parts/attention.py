@@ -53,6 +53,13 @@ class Attention(Mixer):
     def cache_need(spec: AttentionSpec):
         return PagedNeed(spec.num_kv_heads, spec.head_dim, spec.window)
 
+    @staticmethod
+    def workspace_bytes(spec: AttentionSpec, ops, max_requests: int, max_context: int) -> int:
+        sizer = getattr(ops, "attention_scratch_bytes", None)
+        if sizer is None:
+            return 0
+        return sizer(max_requests, spec.num_heads, spec.head_dim, max_context)
+
     def __init__(self, spec: AttentionSpec, tensors, ops, dtype):
         if spec.num_heads % spec.num_kv_heads:
             raise ValueError(f"invalid attention head counts: {spec.num_heads} query, "

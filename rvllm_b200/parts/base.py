@@ -48,6 +48,13 @@ class Mixer:
     def cache_need(spec):
         return None
 
+    @staticmethod
+    def workspace_bytes(spec, ops, max_requests: int, max_context: int) -> int:
+        """Bytes of kernel scratch the mixer's launches can need at most with
+        `max_requests` requests of up to `max_context` cached tokens in a step.  The
+        runner reserves the largest answer once, before it captures any launch sequence."""
+        return 0
+
     def __init__(self, spec, tensors, ops, dtype):
         raise NotImplementedError
 

@@ -7,9 +7,14 @@ computes every formula with ordinary torch CPU tensor operations.
 Where its numbers come from.  The reference project (ermolushka/rvllm) is a Rust
 crate whose dependencies are not available offline, so its model code cannot be
 compiled or imported for a numeric comparison.  Every function below therefore rests
-on the reference's *formulas*; each cites the file and lines it restates.  The
-hand-computed vectors of the reference's own unit tests are restated in
-``tests/test_plain.py`` and anchor the individual formulas.
+on the reference's *formulas*; each cites the file and lines it restates.  Three
+things that execute hold the formulas in place: the hand-computed vectors of the
+reference's own unit tests, restated in ``tests/test_plain.py``; the reference's own
+CUDA kernel sources (short convolution, rotation, SiLU gate, RMSNorm, softmax, argmax,
+cache write and gather, embedding), compiled as C++ and compared function by function
+in ``tests/test_reference_kernels.py`` (their recorded outputs are under
+``tests/golden/``); and a second, independent implementation in float64 NumPy,
+``tests/plain_numpy64.py``, compared on whole models in ``tests/test_plain.py``.
 
 Options that the reference lacks (convolution biases, the feed-forward size rule)
 follow the definitions given in the function that implements them.

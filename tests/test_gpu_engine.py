@@ -156,3 +156,40 @@ def test_repeated_portion_shapes_are_replayed(folders, plains, dtype):
     got = schedules.replay(runner, steps)
     assert runner.graph_steps >= 6 and runner.capture_failures == 0
     compare(got, plains["B"], reqs, dtype)
+
+
+def test_scratch_outgrown_after_a_capture(folders, plains):
+    """A captured decode step names the split-KV scratch by address.  When a later step
+    needs a larger scratch, the old one must stay valid for the older graph: replay it
+    afterwards, with other tensors allocated in between, and compare with the plain
+    implementation; the tensors allocated in between keep their contents."""
+    import gc
+    model, cfg = engine(folders, "B", "bfloat16")
+    ops = model.ops
+    reqs = _requests(cfg.vocab_size, [40], seed=21)
+    ids = reqs["r0"]
+    from rvllm_b200.engine import StepEntry
+    runner = runner_for(model, 16, 8, slots=1, graphs=True)
+    runner.add_request("r0")
+    runner.step([StepEntry("r0", ids[:30], ())])
+    got = {}
+    for p in range(30, 34):                         # captures, then replays, bucket (1, 16)
+        got[("r0", p)] = runner.step([StepEntry("r0", ids[p:p + 1], (0,))])[0].float().cpu()
+    assert runner.graph_steps >= 3
+    before = ops._scratch_buffer(1, model.device)
+    grown = ops._scratch_buffer(4 * before.numel(), model.device)      # a larger step came
+    assert grown.data_ptr() != before.data_ptr()
+    del before, grown
+    gc.collect()
+    torch.cuda.empty_cache()
+    canaries = [torch.full((1 << 18,), 7, dtype=torch.int32, device=model.device)
+                for _ in range(8)]
+    for p in range(34, 40):                         # the old graph again
+        got[("r0", p)] = runner.step([StepEntry("r0", ids[p:p + 1], (0,))])[0].float().cpu()
+    torch.cuda.synchronize()
+    assert all(bool((c == 7).all()) for c in canaries)
+    ref = plains["B"].logits(ids)
+    scale = float(ref.abs().max())
+    for (rid, p), row in got.items():
+        assert float((row - ref[p]).abs().max()) / scale <= BOUND["bfloat16"], p
+    ops.check_status()

@@ -98,6 +98,28 @@ def test_feed_forward_sizes_of_the_published_configs():
 
 
 @pytest.mark.parametrize("name", ["A", "B"])
+def test_agrees_with_the_independent_numpy_implementation(tmp_path, name):
+    """`plain_numpy64.py` restates the architecture a second time, in float64 NumPy with
+    loops and its own reader of the model folder.  Given the same rotation angles the two
+    agree to 1e-11 of the largest logit; with each one's own float32 angle table to 1e-7
+    (two float32 power functions may differ in the last bit of a frequency, which moves an
+    angle by position * 6e-8 relative)."""
+    import plain_numpy64
+    folder = write_tiny(str(tmp_path), name)
+    ids = [(7 * i + 3) % 500 for i in range(40)]
+    a = P.PlainModel(folder, torch.float64).logits(ids).numpy()
+    scale = float(abs(a).max())
+    own = plain_numpy64.logits(folder, ids)
+    assert float(abs(a - own).max()) <= 1e-7 * scale
+    cfg = P.read_config(folder)
+    hd = cfg.get("head_dim") or cfg["hidden_size"] // cfg["num_attention_heads"]
+    cos, sin = P.rope_cos_sin(cfg["rope_theta"], hd, range(len(ids)), torch.float64)
+    same = plain_numpy64.logits(folder, ids, table=lambda t: (cos[t].numpy(), sin[t].numpy()))
+    assert float(abs(a - same).max()) <= 1e-11 * scale
+    assert (a.argmax(-1) == same.argmax(-1)).all()
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
 def test_float32_agrees_with_float64(tmp_path, name):
     folder = write_tiny(str(tmp_path), name)
     ids = [(7 * i + 3) % 500 for i in range(40)]
