@@ -7,7 +7,8 @@ its own key and value tensors [calls, pages, page_size, kv_heads, head_dim] and 
 own block table per request, so a windowed group can give pages back while a
 full-attention group keeps them.  Calls that need a record of fixed size get a
 float32 tensor [slots, *shape]; a request holds one slot id for all of them, even in
-an architecture that has no such call.
+an architecture that has no such call.  A slot's records are zero when a request
+receives it (`add` clears them), so no mixer ever sees its slot's previous holder.
 
 A request's pages are given back when it ends (`free`) and, in a windowed group,
 as soon as every slot of the page lies behind the window of all future queries
@@ -124,6 +125,7 @@ class CacheManager:
         self.requests: Dict[Hashable, RequestCache] = {}
         self._views: List[Optional[CacheView]] = [None] * len(needs)
         call_group: Dict[int, int] = {}
+        state_calls: Dict[tuple, List[int]] = {}
         for i, need in enumerate(needs):
             if isinstance(need, PagedNeed):
                 gi = next((g for g, grp in enumerate(self.groups) if grp.need == need), None)
@@ -133,13 +135,20 @@ class CacheManager:
                 self.groups[gi].calls.append(i)
                 call_group[i] = gi
             elif isinstance(need, StateNeed):
-                if allocate:
-                    self.states[i] = torch.zeros((max_requests,) + tuple(need.shape),
-                                                 dtype=torch.float32, device=device)
-                else:
-                    self.states[i] = None
+                state_calls.setdefault(tuple(need.shape), []).append(i)
+                self.states[i] = None
             elif need is not None:
                 raise CacheError(f"call {i}: unknown cache need {need!r}")
+        # calls whose records have the same shape share one tensor [calls, slots, *shape],
+        # so that a slot is cleared for all of them at once
+        self._state_blocks: List[torch.Tensor] = []
+        if allocate:
+            for shape, calls in state_calls.items():
+                block = torch.zeros((len(calls), max_requests) + shape, dtype=torch.float32,
+                                    device=device)
+                self._state_blocks.append(block)
+                for ci, i in enumerate(calls):
+                    self.states[i] = block[ci]
         for grp in self.groups:
             if allocate:
                 shape = (len(grp.calls), num_pages, page_size, grp.need.num_kv_heads,
@@ -183,6 +192,11 @@ class CacheManager:
         rc = RequestCache(slot=self.slots.alloc(),
                           tables=[PageTable() for _ in self.groups],
                           first_live=[0 for _ in self.groups])
+        # The slot's records read as zero for the new request, whoever held it before: a
+        # mixer's state "before position 0" is part of this contract, not of each mixer.
+        # (In stream order this comes after every step of the slot's previous holder.)
+        for block in self._state_blocks:
+            block[:, rc.slot].zero_()
         self.requests[req] = rc
         return rc
 

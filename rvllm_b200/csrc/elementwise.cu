@@ -68,6 +68,8 @@ extern "C" int rv_embed(const void* table, int dtype, const int* ids, float* out
 //   x = resid[r] + delta[r];  out = x / sqrt(mean(x^2) + eps) * w
 // With `rows` the block reads row rows[m] and leaves the stream untouched (the final
 // norm over the rows whose logits are wanted).
+// Without a stream (`resid` null) the rows of `delta` alone are normalised and nothing is
+// written back: a norm placed after a sub-layer.
 // Reference counterparts: add.cu + rmsnorm.cu + f32_to_f16.cu, three launches.
 template <typename TD, typename TO>
 __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta,
@@ -80,9 +82,9 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restri
     const size_t in = (size_t)(rows ? rows[m] : m) * hidden;
     float ss = 0.f;
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-        float x = resid[in + i];
+        float x = resid ? resid[in + i] : 0.f;
         if (delta) x += rv_load(delta + in + i);
-        if (!rows && delta) resid[in + i] = x;
+        if (!rows && delta && resid) resid[in + i] = x;
         row[i] = x;
         ss += x * x;
     }
@@ -110,12 +112,12 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const TD* __re
     for (int c = 0; c < CHUNKS; ++c) {
         const int i = threadIdx.x + c * blockDim.x;
         if (i < nvec) {
-            x[c] = rv_load4(resid + in + 4 * i);
+            x[c] = resid ? rv_load4(resid + in + 4 * i) : make_float4(0.f, 0.f, 0.f, 0.f);
             w[c] = rv_load4(weight + 4 * i);
             if (delta) {
                 const float4 d = rv_load4(delta + in + 4 * i);
                 x[c].x += d.x; x[c].y += d.y; x[c].z += d.z; x[c].w += d.w;
-                if (!rows) rv_store4(resid + in + 4 * i, x[c]);
+                if (!rows && resid) rv_store4(resid + in + 4 * i, x[c]);
             }
             ss += x[c].x * x[c].x + x[c].y * x[c].y + x[c].z * x[c].z + x[c].w * x[c].w;
         }
@@ -177,6 +179,7 @@ extern "C" int rv_add_rmsnorm(float* resid, const void* delta, int delta_dtype, 
                               float eps, void* stream) {
     if (n_rows == 0) return 0;
     if (n_rows < 0 || hidden <= 0) RV_FAIL("add_rmsnorm: bad sizes");
+    if (!resid && !delta) RV_FAIL("add_rmsnorm: neither a stream nor rows to normalise");
     cudaStream_t s = (cudaStream_t)stream;
     if (delta_dtype == RV_DTYPE_F32 && out_dtype == RV_DTYPE_F32)
         return add_rmsnorm_launch<float, float>(resid, delta, weight, out, rows, n_rows, hidden, eps, s);

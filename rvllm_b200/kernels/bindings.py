@@ -120,17 +120,21 @@ class CudaOps:
     # ---- residual add + RMSNorm ------------------------------------------------------
 
     def add_rmsnorm(self, resid, delta, weight, eps, out, rows=None):
-        self._need(resid, "residual stream", torch.float32)
+        """`resid` None: the rows of `delta` alone are normalised (no stream involved)."""
+        if resid is not None:
+            self._need(resid, "residual stream", torch.float32)
+        elif delta is None or rows is not None:
+            raise KernelError("add_rmsnorm: without a stream it takes rows to normalise, all of them")
         self._need(weight, "norm weight", torch.float32)
         self._need(out, "norm output")
         if delta is not None:
             self._need(delta, "pending sub-layer output")
-            if delta.shape != resid.shape:
+            if resid is not None and delta.shape != resid.shape:
                 raise KernelError("add_rmsnorm: the stream and the pending output differ in shape")
         if rows is not None:
             self._need(rows, "row list", torch.int32)
         n, hidden = out.shape
-        if resid.shape[1] != hidden or weight.shape[0] != hidden:
+        if (resid if resid is not None else delta).shape[1] != hidden or weight.shape[0] != hidden:
             raise KernelError("add_rmsnorm: widths disagree")
         self._check(self.lib.rv_add_rmsnorm(
             _ptr(resid), _ptr(delta), _code(delta.dtype) if delta is not None else _F32,

@@ -47,11 +47,11 @@ def build_spec(cfg: Lfm2Config) -> ModelSpec:
         layers.append(BlockSpec(
             arrangement="pre_norm",
             mixer=attention if is_attn else conv,
-            feed_forward=ffn, mixer_norm=norm, ffn_norm=norm,
+            feed_forward=ffn,
+            norms={"mixer": (norm, p + "operator_norm.weight"),
+                   "ffn": (norm, p + "ffn_norm.weight")},
             mixer_prefix=p + ("self_attn." if is_attn else "conv."),
-            ffn_prefix=p + "feed_forward.",
-            mixer_norm_name=p + "operator_norm.weight",
-            ffn_norm_name=p + "ffn_norm.weight"))
+            ffn_prefix=p + "feed_forward."))
     return ModelSpec(
         architecture=cfg.architecture, vocab_size=cfg.vocab_size, hidden=hidden,
         max_position=cfg.max_position_embeddings, layers=tuple(layers),

@@ -27,7 +27,9 @@ class PagedNeed:
 
 @dataclass(frozen=True)
 class StateNeed:
-    """A float32 record of this shape per live request; zero before position 0."""
+    """A float32 record of this shape per live request.  The cache manager hands a request
+    its slot with the record cleared to zero, so the state before position 0 is zero
+    without the mixer's doing."""
     shape: Tuple[int, ...]
 
 
@@ -79,7 +81,8 @@ class FeedForward:
 class Norm:
     """norm.add_norm(resid, delta, ctx, rows=None) adds `delta` (or nothing) to the
     float32 residual stream in place and returns the normalised rows in the compute
-    dtype; with `rows` it reads only those rows and leaves the stream untouched."""
+    dtype; with `rows` it reads only those rows and leaves the stream untouched.
+    norm.norm(x, ctx) normalises rows that are not part of the stream."""
 
     @staticmethod
     def params(spec) -> Dict[str, ParamDecl]:
@@ -89,6 +92,11 @@ class Norm:
         raise NotImplementedError
 
     def add_norm(self, resid, delta, ctx, rows=None):
+        raise NotImplementedError
+
+    def norm(self, x, ctx):
+        """The normalised rows of `x` (compute dtype), with no residual stream involved:
+        what a norm placed after a sub-layer applies to its output."""
         raise NotImplementedError
 
 

@@ -21,9 +21,12 @@ class ParamDecl:
     """One tensor a part needs.
 
     shape      shape the part works with
-    init       distribution of the random-weights mode:
+    init       distribution of the random-weights mode, by name:
                "linear" and "embedding" N(0, 0.02), "conv" N(0, 0.2),
-               "norm" 1 + N(0, 0.05), "bias" N(0, 0.02), "zeros"
+               "norm" 1 + N(0, 0.05), "bias" N(0, 0.02), "zeros";
+               or "normal" with the part's own `mean` and `std`
+    mean, std  given, they replace the named distribution's values, so a part outside
+               this package can ask for any normal distribution
     alt_shapes shapes a file may store instead (same element count; reshaped on load)
     integer    an integer table: kept as int32 whatever the compute dtype
     """
@@ -31,6 +34,8 @@ class ParamDecl:
     init: str
     alt_shapes: Tuple[Tuple[int, ...], ...] = ()
     integer: bool = False
+    mean: Optional[float] = None
+    std: Optional[float] = None
 
 
 @dataclass(frozen=True)
@@ -91,19 +96,20 @@ class SwiGLUSpec(FeedForwardSpec):
 class BlockSpec:
     """One layer: which parts and how they are arranged.
 
-    arrangement "pre_norm": h = x + mixer(norm(x)); out = h + ffn(norm(h))
-    (src/model.rs:556-585).  The *_prefix / *_name fields say where the parts'
-    tensors are found in the file.
+    `norms` maps a place in the block to (norm spec, tensor name in the file); which
+    places exist is the arrangement's business.  "pre_norm" (src/model.rs:556-585):
+        h = x + post_mixer(mixer(mixer_norm(x)));  out = h + post_ffn(ffn(ffn_norm(h)))
+    with places "mixer" and "ffn" required and "post_mixer", "post_ffn" optional (the
+    reference's `post_attn_norm` and `post_ffn_norm`, src/model.rs:571, 581; LFM2 has
+    neither).  The *_prefix fields say where the mixer's and the feed-forward's tensors
+    are found in the file.
     """
     arrangement: str
     mixer: MixerSpec
     feed_forward: FeedForwardSpec
-    mixer_norm: NormSpec
-    ffn_norm: NormSpec
-    mixer_prefix: str
-    ffn_prefix: str
-    mixer_norm_name: str
-    ffn_norm_name: str
+    norms: Mapping[str, Tuple[NormSpec, str]] = field(hash=False)
+    mixer_prefix: str = ""
+    ffn_prefix: str = ""
 
 
 @dataclass(frozen=True)

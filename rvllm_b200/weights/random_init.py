@@ -2,7 +2,8 @@
 configuration and a seed.
 
 Distributions: matrices and the embedding N(0, 0.02); convolution filters N(0, 0.2);
-norm weights 1 + N(0, 0.05); biases N(0, 0.02).  Each tensor draws from its own
+norm weights 1 + N(0, 0.05); biases N(0, 0.02); a declaration may carry a mean and a
+standard deviation of its own instead (`ParamDecl.mean`, `.std`).  Each tensor draws from its own
 generator, keyed by the seed and the tensor's name, so a tensor's values do not
 depend on which other tensors the model has.  Values are stored in the
 configuration's `torch_dtype`.  (The reference has no such mode; its tests build
@@ -36,11 +37,14 @@ def random_tensor(name: str, decl: ParamDecl, seed: int, dtype: torch.dtype) -> 
         return torch.randint(0, 2 ** 15, decl.shape, generator=gen, dtype=torch.int32)
     if decl.init == "zeros":
         return torch.zeros(decl.shape, dtype=dtype)
-    if decl.init not in _STD:
-        raise ValueError(f"tensor {name!r}: unknown initialisation {decl.init!r}")
-    t = torch.randn(decl.shape, generator=gen, dtype=torch.float32) * _STD[decl.init]
-    if decl.init == "norm":
-        t = t + 1.0
+    if decl.init not in _STD and (decl.init != "normal" or decl.std is None):
+        raise ValueError(f"tensor {name!r}: unknown initialisation {decl.init!r} (a named "
+                         f"one of {sorted(_STD)} or zeros, or \"normal\" with its own std)")
+    std = decl.std if decl.std is not None else _STD[decl.init]
+    mean = decl.mean if decl.mean is not None else (1.0 if decl.init == "norm" else 0.0)
+    t = torch.randn(decl.shape, generator=gen, dtype=torch.float32) * std
+    if mean != 0.0:
+        t = t + mean
     return t.to(dtype)
 
 

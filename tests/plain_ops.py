@@ -30,7 +30,9 @@ class PlainOps:
 
     # ---- residual add + RMSNorm ------------------------------------------------------
     def add_rmsnorm(self, resid, delta, weight, eps, out, rows=None):
-        if rows is None:
+        if resid is None:
+            x = _f(delta)
+        elif rows is None:
             if delta is not None:
                 resid.add_(_f(delta))
             x = resid

@@ -291,6 +291,79 @@ def test_paged_attention(ops, dtype, case, standout):
     assert torch.allclose(out2.cpu().float(), ref.float(), **t)
 
 
+EDGE_CASES = [
+    # q_len, context, window, page: where the window's first key `lo` of the last (and, for a
+    # portion, of the first) query falls
+    (1, 356, 100, 16),      # lo = 256: a split, tile and page boundary
+    (1, 321, 129, 16),      # lo = 192: a tile boundary inside a split
+    (1, 258, 50, 16),       # lo = 208: a page boundary inside a tile
+    (1, 356, 100, 64),      # lo = 256 with pages of 64
+    (8, 356, 100, 16),      # portion: last query lo = 256
+    (8, 363, 100, 16),      # portion: first query lo = 256
+    (8, 328, 129, 8),       # portion: first query lo = 192, last 199
+    (40, 300, 37, 32),      # portion longer than the window
+]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("case", EDGE_CASES)
+def test_window_edge(ops, dtype, case):
+    """The first key of a window must count and the key before it must not.  For the first
+    and the last query of each request the key at `lo` is made to dominate the softmax, and
+    the key at `lo - 1` is made twice as strong again with a value far from all others: a
+    kernel that is off by one at the window's edge returns another vector altogether, not a
+    slightly different average.  Every attention kernel that can take the case runs it."""
+    q_len, clen, window, ps = case
+    nh, nkv, hd = 4, 2, 64
+    g = torch.Generator().manual_seed(31)
+    q_lens, ctx_lens = [q_len, q_len], [clen, clen - 64]
+    q, kc, vc, ctx, group = attention_case(dtype, g, q_lens, ctx_lens, nh, nkv, hd, ps, window)
+    q_start = ctx.q_start.tolist()
+    for r in range(2):
+        for t, p in ((q_start[r], ctx_lens[r] - q_len), (q_start[r + 1] - 1, ctx_lens[r] - 1)):
+            lo = p - window + 1
+            assert lo >= 1
+            for h in range(nh):
+                qh = q[t, h * hd:(h + 1) * hd].float()
+                for key, strength in ((lo, 6.0), (lo - 1, 12.0)):
+                    page, slot = int(group.block_table[r, key // ps]), key % ps
+                    kc[page, slot, h // (nh // nkv)] = (qh / qh.norm() * strength).to(dtype)
+                    if key == lo - 1:
+                        vc[page, slot, h // (nh // nkv)] = 50.0
+    scale = 1.0 / math.sqrt(hd)
+    ref = torch.zeros(ctx.n_tokens, nh * hd, dtype=dtype)
+    PlainOps().paged_attention(q, nh, nkv, hd, kc, vc, ctx, group, scale, window, ref)
+    wrong = torch.zeros_like(ref)
+    PlainOps().paged_attention(q, nh, nkv, hd, kc, vc, ctx, group, scale, window + 1, wrong)
+    assert float((wrong.float() - ref.float()).abs().max()) > 10       # the edge decides the result
+    dq, dk, dv, dctx, dgroup = q.cuda(), kc.cuda(), vc.cuda(), to_cuda(ctx), to_cuda(group)
+    t = dict(atol=3e-5, rtol=1e-4) if dtype == torch.float32 else dict(atol=3e-2, rtol=2e-2)
+
+    def run(label):
+        out = torch.full((ctx.n_tokens, nh * hd), float("nan"), dtype=dtype, device="cuda")
+        ops.paged_attention(dq, nh, nkv, hd, dk, dv, dctx, dgroup, scale, window, out)
+        assert torch.allclose(out.cpu().float(), ref.float(), **t), label
+
+    run("chosen by size")
+    if dtype == torch.bfloat16:
+        chosen = ops.decode_kernel, ops.prefill_attention
+        try:
+            if q_len == 1:
+                for kernel in ("block", "stream"):
+                    ops.decode_kernel = kernel
+                    run(kernel)
+            else:
+                for kernel in ("tcgen05", "mma"):
+                    ops.prefill_attention = kernel
+                    run(kernel)
+            ops.check_status()
+        finally:
+            ops.decode_kernel, ops.prefill_attention = chosen
+    out2 = torch.full((ctx.n_tokens, nh * hd), float("nan"), dtype=dtype, device="cuda")
+    ops.paged_attention_general(dq, nh, nkv, hd, dk, dv, dctx, dgroup, scale, window, out2)
+    assert torch.allclose(out2.cpu().float(), ref.float(), **t)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_paged_attention_padding_rows(ops, dtype):
     """Requests with context 0 are padding: zeros out, nothing read."""

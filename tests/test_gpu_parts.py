@@ -161,8 +161,9 @@ def test_pre_norm_block(ops, dtype):
     spec = BlockSpec("pre_norm", ShortConvSpec("short_conv", hidden, taps=3, bias=False),
                      SwiGLUSpec("swiglu", hidden, ffn_dim=96,
                                 names={"gate": "w1.weight", "up": "w3.weight", "down": "w2.weight"}),
-                     norm, norm, "model.layers.0.conv.", "model.layers.0.feed_forward.",
-                     "model.layers.0.operator_norm.weight", "model.layers.0.ffn_norm.weight")
+                     {"mixer": (norm, "model.layers.0.operator_norm.weight"),
+                      "ffn": (norm, "model.layers.0.ffn_norm.weight")},
+                     "model.layers.0.conv.", "model.layers.0.feed_forward.")
     cls = arrangement_class("pre_norm")
     dev, host = tensors_for(cls.params(spec), dtype)
     block = cls(spec, dev, ops, dtype)

@@ -59,3 +59,46 @@ def test_toy_under_every_cut(setup, schedule):
     if schedule != "whole":      # a whole prompt reserves all its pages at once
         assert windowed.pool.high_water < full.pool.high_water   # the window gave pages back
     assert all(g.pool.in_use == 0 for g in cache.groups)
+
+
+def test_a_reused_slot_starts_from_zero(setup):
+    """One state slot, two requests one after the other: the second gets the slot the first
+    left full of its state, and `ToyDecay` does nothing to clear it.  Its logits are those
+    of a fresh sequence because the cache manager clears a slot when it hands it out."""
+    model, w = setup
+    rng = random.Random(3)
+    first = [rng.randrange(300) for _ in range(30)]
+    second = [rng.randrange(300) for _ in range(18)]
+    cache = make_cache(model, 4, 32, 1)
+    runner = ModelRunner(model, cache, PlainOps())
+    from rvllm_b200.engine import StepEntry
+    runner.add_request("a")
+    slot = cache.requests["a"].slot
+    runner.step([StepEntry("a", first, ())])
+    assert float(cache.states[0][slot].abs().max()) > 0
+    runner.end_request("a")
+    runner.add_request("b")
+    assert cache.requests["b"].slot == slot
+    got = runner.step([StepEntry("b", second, range(len(second)))])
+    ref = toy.toy_plain_logits(second, w, toy.TOY)
+    assert torch.allclose(got.cpu(), ref, atol=2e-5, rtol=0)
+
+
+def test_post_norms_and_own_distribution(setup):
+    model, w = setup
+    assert model.blocks[3].post_mixer is not None and model.blocks[3].post_ffn is not None
+    assert model.blocks[0].post_mixer is None
+    assert "blocks.3.post1.weight" in w and "blocks.0.post1.weight" not in w
+    std = float(w["blocks.0.mixer.w.weight"].std())
+    assert 0.025 < std < 0.035            # N(0, 0.03) as the part declared, not a named kind
+
+
+def test_a_place_the_arrangement_does_not_know_is_refused():
+    from rvllm_b200.parts import BlockSpec, NormSpec, arrangement_class
+    norm = NormSpec("rmsnorm", 8, 1e-5)
+    spec = BlockSpec("pre_norm", toy.ToyDecaySpec("toy_decay", 8),
+                     toy.ScaledReluSpec("toy_scaled_relu", 8, width=8),
+                     {"mixer": (norm, "a"), "ffn": (norm, "b"), "middle": (norm, "c")}, "m.", "f.")
+    toy.register_toy()
+    with pytest.raises(ValueError, match="no place 'middle'"):
+        arrangement_class("pre_norm").params(spec)

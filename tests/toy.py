@@ -2,14 +2,17 @@
 architectures plug in without touching the package:
 
 * `ToyDecay`, a mixer with a state of its own (one float32 vector per request):
-  s_t = decay * s_{t-1} + W x_t, out_t = s_t;
+  s_t = decay * s_{t-1} + W x_t, out_t = s_t; it relies on the cache manager's promise
+  that a slot is zero when a request receives it, and its weight asks the random-weights
+  mode for a distribution of its own;
 * `ScaledRelu`, another feed-forward: down(relu(up(x)) * gain);
 * `SoftRouted`, a feed-forward with a router: float32 router logits, softmax gates over
   its experts, out = sum_e gate_e * down_e(relu(up_e(x))) (every expert weighted, so the
   result is continuous in the logits and a test cannot flip on a near-tie);
 * `HalfRope`, another position encoding: the reference rotation at half the angle;
 * "ToyForCausalLM": blocks [decay, windowed attention with HalfRope, attention without
-  position encoding or q/k norm and a custom scale, decay with the routed feed-forward],
+  position encoding or q/k norm and a custom scale, decay with the routed feed-forward and
+  norms after the mixer and after the feed-forward as well as before them],
   run in the order
   0, 1, 2, 1(reading nothing: a second call with its own cache), 3, 2(reading the cache
   of the first call of block 2), so a block runs twice and a call reads another call's
@@ -42,7 +45,8 @@ class ToyDecaySpec(MixerSpec):
 class ToyDecay(Mixer):
     @staticmethod
     def params(spec, owns_cache=True):
-        return {"w.weight": ParamDecl((spec.hidden, spec.hidden), "linear")}
+        # a distribution of its own for the random-weights mode
+        return {"w.weight": ParamDecl((spec.hidden, spec.hidden), "normal", mean=0.0, std=0.03)}
 
     @staticmethod
     def cache_need(spec):
@@ -57,11 +61,12 @@ class ToyDecay(Mixer):
         out = torch.empty_like(y)
         starts = ctx.q_start.tolist()
         slots = ctx.state_slot.tolist()
-        first = ctx.start_pos.tolist()
         for r in range(ctx.n_reqs):
             if slots[r] < 0:
                 continue
-            s = cache.state[slots[r]] if first[r] > 0 else torch.zeros_like(cache.state[slots[r]])
+            # no test of "is this the request's first step": the cache manager hands out a
+            # slot cleared to zero, so the state before position 0 is simply what is there
+            s = cache.state[slots[r]]
             for t in range(starts[r], starts[r + 1]):
                 s = self.spec.decay * s + y[t]
                 out[t] = s
@@ -186,8 +191,12 @@ def toy_spec(cfg: ToyConfig) -> ModelSpec:
     layers = []
     for i, mixer in enumerate([decay, local, plain, decay]):
         p = f"blocks.{i}."
-        layers.append(BlockSpec("pre_norm", mixer, routed if i == 3 else ffn, norm, norm,
-                                p + "mixer.", p + "ffn.", p + "norm1.weight", p + "norm2.weight"))
+        norms = {"mixer": (norm, p + "norm1.weight"), "ffn": (norm, p + "norm2.weight")}
+        if i == 3:      # this block also normalises what its mixer and feed-forward give back
+            norms["post_mixer"] = (norm, p + "post1.weight")
+            norms["post_ffn"] = (norm, p + "post2.weight")
+        layers.append(BlockSpec("pre_norm", mixer, routed if i == 3 else ffn, norms,
+                                p + "mixer.", p + "ffn."))
     return ModelSpec(architecture=cfg.architecture, vocab_size=cfg.vocab_size, hidden=cfg.hidden,
                      max_position=cfg.max_position, layers=tuple(layers),
                      order=tuple(LayerCall(b, c) for b, c in ORDER), final_norm=norm,
@@ -261,6 +270,11 @@ def toy_plain_logits(ids, w: Dict[str, torch.Tensor], cfg: dict) -> torch.Tensor
             scale = None if b == 1 else 0.3
             o = P.gqa_attention(q, kk, vv, P.causal_mask(n, window, torch.float32), scale)
             mixed = P.linear(o.transpose(0, 1).reshape(n, nh * hd), w[m + "out_proj.weight"])
+        if p + "post1.weight" in w:
+            mixed = P.rms_norm(mixed, w[p + "post1.weight"], eps)
         h = x + mixed
-        x = h + ffn(P.rms_norm(h, w[p + "norm2.weight"], eps), p + "ffn.")
+        out = ffn(P.rms_norm(h, w[p + "norm2.weight"], eps), p + "ffn.")
+        if p + "post2.weight" in w:
+            out = P.rms_norm(out, w[p + "post2.weight"], eps)
+        x = h + out
     return P.linear(P.rms_norm(x, w["norm.weight"], eps), w["head.weight"])
