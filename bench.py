@@ -18,7 +18,20 @@ steps it holds 4096 - K tokens, then K steps are timed with CUDA events and end 
              the bfloat16 peak
   roofline   the decode step's bytes (every weight once, the live requests' keys and
              values and convolution states) / its time, against the HBM peak
-  points     decoded tokens a second at batch 1 and batch 64 (context 2,048 + steps)
+  points     decoded tokens a second at batch 1 and batch 64 (context 2,048 + steps), each
+             with its bytes / time as a fraction of the HBM peak (`decode_b1_frac`, ...)
+  workloads  two scheduler runs through `Engine.step` with requests that come and go
+             (`--workloads none` leaves them out; `--only workload --workload NAME` runs one):
+             350m-mixed      LFM2-350M sizes, 32 requests, prompts U[128, 2048], prompt
+                             portions of 512 beside the running decodes, 256 new tokens each
+             700m-staggered  LFM2-700M sizes, 64 requests arriving four steps apart, prompts
+                             U[512, 8192], 512 new tokens each, a page pool of 90 % of the
+                             free device memory
+             each after one untimed run of the same requests: output and total tokens a
+             second, steps, preemptions, the share of steps replayed from a captured graph,
+             and per step the host time of `Engine.step` against the device time between
+             events recorded around it (`gpu_idle_frac`: the share of the run's wall time in
+             which the device waited for the host)
 
 RVLLM_BENCH_PAGE sets the tokens per cache page (16; 64 measured the same).
 
@@ -51,6 +64,13 @@ SIZES = {
     "1.2b": {},
     "700m": {"hidden_size": 1536, "num_attention_heads": 24, "block_ff_dim": 10240},
     "350m": {"hidden_size": 1024, "num_attention_heads": 16, "block_ff_dim": 6656},
+}
+WORKLOADS = {
+    "350m-mixed": {"size": "350m", "requests": 32, "prompt": (128, 2048), "new": 256,
+                   "chunk": 512, "arrival_gap": 0, "pool": "fit", "positions": 4096},
+    "700m-staggered": {"size": "700m", "requests": 64, "prompt": (512, 8192), "new": 512,
+                       "chunk": 2048, "arrival_gap": 4, "pool": "90% of free HBM",
+                       "positions": 16384},
 }
 CONTEXT = 4096
 PREFILL_TOKENS = 2048
@@ -284,8 +304,19 @@ def run_ours(args):
     for b in (1, 64):
         # 2,048 prompt tokens, then 8 untimed steps: the padded block-table width grows at
         # 2,049 tokens, and the graph of the new width is captured there, outside the timing
-        v, _, _ = timed_decode(b, 2048 + 8, 256, 8)
+        v, ms, _ = timed_decode(b, 2048 + 8, 256, 8)
         points[f"decode_b{b}"] = round(v, 1)
+        nbytes = weight_bytes + b * (2048 + 8 + 128) * kv_bytes_per_token + b * conv_state_bytes
+        points[f"decode_b{b}_frac"] = round(nbytes / (ms / 1e3) / 1e9 / pk["hbm_gbs"], 4)
+
+    del model
+    workloads = {}
+    if args.workloads != "none":
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+        for name in (WORKLOADS if args.workloads == "both" else [args.workloads]):
+            workloads[name] = run_workload(name)
 
     line = {
         "metric": f"decode tok/s at batch {B} (LFM2-{args.size.upper()} sizes, context to 4,096)",
@@ -304,7 +335,7 @@ def run_ours(args):
         "e2e": e2e, "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"],
                      "unit": "GB/s", "frac": round(achieved / pk["hbm_gbs"], 4)},
-        "points": points, "gpu_launches": launches, "clocks": clocks,
+        "points": points, "workloads": workloads, "gpu_launches": launches, "clocks": clocks,
         "setup_s": round(setup_s, 1),
     }
     print(json.dumps(line))
@@ -464,6 +495,100 @@ def run_kernels(args):
     return 0
 
 
+def run_workload(name, verbose=False):
+    """One scheduler workload through `Engine.step`, after an untimed run of the same
+    requests (the reference's bench discards a warm-up run too, src/bin/bench.rs:215-232;
+    prompts are seeded uniform random ids like its own, src/bin/bench.rs:93-109; random
+    weights never produce a meaningful stop token, so none is set and every request
+    generates its full length)."""
+    import random
+
+    import torch
+
+    from rvllm_b200.config import config_from_dict
+    from rvllm_b200.engine import (Engine, ModelRunner, Request, SchedulerConfig, graphs_default,
+                                   load_model, make_cache)
+    from rvllm_b200.sampling import SamplingParams
+    from rvllm_b200.weights import write_random_model
+
+    w = WORKLOADS[name]
+    data = dict(LFM2_1_2B)
+    data.update(SIZES[w["size"]])
+    data["max_position_embeddings"] = w["positions"]
+    cfg = config_from_dict(data)
+    tmp = tempfile.mkdtemp(prefix="rvllm_bench_")
+    try:
+        folder = write_random_model(os.path.join(tmp, "model"), cfg, seed=0)
+        model, cfg = load_model(folder, "bfloat16", "cuda")
+    finally:
+        shutil.rmtree(tmp, ignore_errors=True)
+    rng = random.Random(17)
+    lengths = [rng.randint(*w["prompt"]) for _ in range(w["requests"])]
+    prompts = [[rng.randrange(cfg.vocab_size) for _ in range(n)] for n in lengths]
+    per_token = 2 * len(cfg.full_attn_idxs) * cfg.num_key_value_heads * cfg.head_dim * 2
+    if w["pool"] == "fit":
+        pages = sum(-(-(n + w["new"]) // PAGE) for n in lengths)
+    else:
+        torch.cuda.synchronize()
+        free, _ = torch.cuda.mem_get_info()
+        pages = int(0.9 * free) // (per_token * PAGE)
+    cache = make_cache(model, PAGE, pages, w["requests"])
+    runner = ModelRunner(model, cache, model.ops, use_graphs=graphs_default())
+    sched = SchedulerConfig(block_size=PAGE, num_blocks=pages,
+                            max_num_batched_tokens=w["chunk"] + w["requests"],
+                            prefill_chunk=w["chunk"])
+
+    def one_run(timed):
+        engine = Engine(runner, sched, cfg.max_position_embeddings, lookahead=True)
+        for i, ids in enumerate(prompts):
+            engine.add_request(Request(i, ids, w["new"], (), SamplingParams(),
+                                       arrival_step=i * w["arrival_gap"]))
+        steps0, graph0 = runner.steps, runner.graph_steps
+        marks, host = [], []
+        out_tokens = 0
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        while engine.has_work():
+            a = torch.cuda.Event(enable_timing=True)
+            b = torch.cuda.Event(enable_timing=True)
+            a.record()
+            h0 = time.perf_counter()
+            out_tokens += len(engine.step())
+            host.append(time.perf_counter() - h0)
+            b.record()
+            marks.append((a, b))
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - t0
+        model.ops.check_status()
+        if not timed:
+            return None
+        device = [a.elapsed_time(b) for a, b in marks]
+        st = engine.scheduler.stats
+        n_steps = runner.steps - steps0
+        busy = sum(device) / 1e3
+        return {
+            "model": f"LFM2-{w['size'].upper()} sizes", "requests": w["requests"],
+            "prompt_tokens": sum(lengths), "new_tokens": out_tokens,
+            "pool_pages": pages, "pool": w["pool"],
+            "wall_s": round(wall, 3),
+            "output_tok_s": round(out_tokens / wall, 1),
+            "total_tok_s": round((sum(lengths) + out_tokens) / wall, 1),
+            "steps": n_steps, "preemptions": st.preemptions,
+            "graph_step_share": round((runner.graph_steps - graph0) / max(1, n_steps), 3),
+            "host_ms_per_step": round(1e3 * sum(host) / len(host), 3),
+            "device_ms_per_step": round(sum(device) / len(device), 3),
+            "gpu_idle_frac": round(max(0.0, 1.0 - busy / wall), 3),
+        }
+
+    one_run(False)
+    result = one_run(True)
+    del runner, cache, model
+    import gc
+    gc.collect()
+    torch.cuda.empty_cache()
+    return result
+
+
 def run_reference(args):
     print(json.dumps({
         "impl": "reference",
@@ -481,8 +606,12 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--size", default="1.2b", choices=sorted(SIZES),
                     help="layer sizes: LFM2-1.2B (the default and the headline), 700M or 350M")
-    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "kernels", "breakdown"],
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "kernels", "breakdown", "workload"],
                     help="run one part only (for profiling); the JSON line then lacks the rest")
+    ap.add_argument("--workloads", default="both", choices=["both", "none"] + sorted(WORKLOADS),
+                    help="scheduler workloads to add to the line (default: both)")
+    ap.add_argument("--workload", default="350m-mixed", choices=sorted(WORKLOADS),
+                    help="with --only workload: which one")
     ap.add_argument("--kernel", default="all",
                     help="with --only kernels: attn_decode, attn_prefill, gemm, gemm:NxK or all")
     ap.add_argument("--kernel-batch", type=int, default=64)
@@ -497,6 +626,9 @@ def main():
         args.warmup = 3
     if args.only == "kernels":
         return run_kernels(args)
+    if args.only == "workload":
+        print(json.dumps({"only": "workload", args.workload: run_workload(args.workload)}))
+        return 0
     return run_ours(args)
 
 
