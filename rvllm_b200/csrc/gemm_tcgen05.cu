@@ -24,94 +24,12 @@
 //
 // Reference counterpart: `linear_f16` = cublasGemmEx (src/cuda/cublas_ops.rs:44-92).
 // Plain reference: tests/plain_ops.py linear.
-#include <cuda.h>
-
-#include "common.cuh"
+#include "tcgen05_common.cuh"
 
 #define RV_GEMM_BM 128          // rows of W per block (the MMA's M)
 #define RV_GEMM_BK 64           // K elements per stage: 128 bytes, one swizzle row
 #define RV_GEMM_MAX_STAGES 12
 #define RV_GEMM_SMEM_LIMIT (226 * 1024)
-#define RV_WAIT_CYCLES 400000000ll   // about 0.2 s: far beyond any real wait
-
-typedef __nv_bfloat16 bf16;
-
-// ---- PTX wrappers ---------------------------------------------------------------------
-__device__ __forceinline__ unsigned smem_u32(const void* p) {
-    return (unsigned)__cvta_generic_to_shared(p);
-}
-__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
-                 "r"(bytes)
-                 : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned parity) {
-    unsigned done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.b32 %0, 1, 0, p;\n\t}"
-        : "=r"(done)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-    return done != 0;
-}
-// Bounded wait: false when the time limit ran out or another thread already gave up.  The
-// bound is in clock cycles because a single poll may block for a while inside the hardware.
-__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity,
-                                          volatile int* failed) {
-    if (mbar_try_wait(bar, parity)) return true;             // the common case: no clock read
-    const long long start = clock64();
-    for (unsigned i = 1;; ++i) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if (*failed) return false;
-        if ((i & 63u) == 0 && clock64() - start > RV_WAIT_CYCLES) return false;
-    }
-}
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map,
-                                            unsigned long long* bar, int c0, int c1) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
-        " [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(smem_u32(dst)), "l"((unsigned long long)map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
-        : "memory");
-}
-__device__ __forceinline__ void tcgen05_commit(unsigned long long* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
-                 ::"r"(smem_u32(bar))
-                 : "memory");
-}
-__device__ __forceinline__ void tcgen05_mma_f16(unsigned tmem_d, unsigned long long a_desc,
-                                                unsigned long long b_desc, unsigned idesc,
-                                                unsigned accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-        ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
-        : "memory");
-}
-__device__ __forceinline__ void tmem_load_16(unsigned taddr, unsigned (&r)[16]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, "
-        "%12, %13, %14, %15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
-          "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
-// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of 128
-// bytes, groups of 8 rows 1024 bytes apart (stride byte offset), leading byte offset
-// unused (1), descriptor version 1, layout type 2 (SWIZZLE_128B).
-__device__ __forceinline__ unsigned long long smem_desc_sw128(const void* tile) {
-    const unsigned long long addr = (smem_u32(tile) & 0x3FFFFu) >> 4;
-    return addr | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
-}
 
 // ---- the kernel -----------------------------------------------------------------------
 // grid (n_tiles, splits) with clusters of (1, splits); block 128 threads.
@@ -366,39 +284,6 @@ __global__ void __launch_bounds__(128) gemm_tcgen05_kernel(
         }
     }
     cluster_sync_relaxed();                                   // nobody leaves while it is read
-}
-
-// ---- host side ----------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
-                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    if (!fn) {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) ==
-                cudaSuccess && q == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)p;
-    }
-    return fn;
-}
-
-// A [rows, K] bfloat16 row-major matrix seen through boxes of [box_rows, 64].
-static int make_map(CUtensorMap* map, const void* ptr, long long rows, long long K, int box_rows) {
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) RV_FAIL("gemm_tcgen05: cuTensorMapEncodeTiled is not available in this driver");
-    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)K * 2};
-    cuuint32_t box[2] = {RV_GEMM_BK, (cuuint32_t)box_rows};
-    cuuint32_t elem[2] = {1, 1};
-    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides,
-                    box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) RV_FAIL("gemm_tcgen05: cuTensorMapEncodeTiled failed with code %d", (int)r);
-    return 0;
 }
 
 static int env_int(const char* name, int fallback) {
