@@ -432,6 +432,37 @@ def run_kernels(args):
             ts.append(e0.elapsed_time(e1) * 1e3 / len(fns))
         return sorted(ts)[len(ts) // 2]
 
+    if args.kernel == "copy_rate":
+        # the copy probe (csrc/copy_probe.cu): what one SM, a quarter of the SMs and all of
+        # them can copy into shared memory, as tensor-map boxes and as contiguous bulk copies
+        import ctypes
+        K, iters = 2048, 512
+        sms = torch.cuda.get_device_properties(0).multi_processor_count
+        rows = sms * iters * 16384 // (K * 2) + 128
+        w = torch.randn(rows, K, device="cuda", dtype=torch.bfloat16)      # 1.2 GB: larger than L2
+        status = ops.status_word("cuda")
+        for mode, name in ((0, "box"), (1, "bulk")):
+            for grid in (sms, sms // 4, 1):
+                for stages in (4, 10):
+                    def call():
+                        ops._check(ops.lib.rv_copy_probe(
+                            ctypes.c_void_p(w.data_ptr()), ctypes.c_longlong(rows), ctypes.c_int(K),
+                            ctypes.c_int(mode), ctypes.c_int(grid), ctypes.c_int(iters),
+                            ctypes.c_int(stages), ctypes.c_void_p(status.data_ptr()),
+                            ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)), "copy_probe")
+                    call()
+                    torch.cuda.synchronize()
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                    call()
+                    e1.record()
+                    torch.cuda.synchronize()
+                    gbs = grid * iters * 16384 / (e0.elapsed_time(e1) * 1e-3) / 1e9
+                    out[f"copy_{name}_sms{grid}_stages{stages}"] = {
+                        "GB/s": round(gbs, 1), "GB/s_per_sm": round(gbs / grid, 1)}
+        ops.check_status()
+        print(json.dumps(out))
+        return 0
     if args.kernel in ("all", "attn_decode"):
         B, ctx = args.kernel_batch, args.kernel_ctx
         blocks = -(-ctx // ps)
@@ -613,7 +644,7 @@ def main():
     ap.add_argument("--workload", default="350m-mixed", choices=sorted(WORKLOADS),
                     help="with --only workload: which one")
     ap.add_argument("--kernel", default="all",
-                    help="with --only kernels: attn_decode, attn_prefill, gemm, gemm:NxK or all")
+                    help="with --only kernels: attn_decode, attn_prefill, gemm, gemm:NxK, copy_rate or all")
     ap.add_argument("--kernel-batch", type=int, default=64)
     ap.add_argument("--kernel-ctx", type=int, default=4096)
     args = ap.parse_args()

@@ -286,7 +286,6 @@ class _DecodeGraph:
         self.dev = torch.empty(words, dtype=torch.int32, device=runner.device)
         self.graph = None
         self.logits = None
-        self.program = None
         self.broken = False
         self.capturing = False
 
@@ -306,26 +305,16 @@ class _DecodeGraph:
             # writes to no cache (a second run of real tokens would shift the
             # convolution states twice).
             warm = self._build([])
-            # Steps of few tokens run as a step program where the model's parts can describe
-            # themselves to one: a few resident launches instead of one launch per operation.
-            # It is built on this graph's own index arrays, whose addresses never change.
-            build = getattr(model, "build_program", None)
-            self.program = build(warm, views) if build is not None else None
-            step = self.program.run if self.program is not None else \
-                (lambda: model.forward(warm, views))
-            step()
+            model.forward(warm, views)
             torch.cuda.synchronize()
-            model.ops.check_status()
             ctx = self._build(entries)
             if device_tokens is not None:
                 ctx.token_ids[:len(entries)].copy_(device_tokens)
             launches = model.ops.launches
             graph = torch.cuda.CUDAGraph()
             self.capturing = True
-            if self.program is None:
-                step = lambda: model.forward(ctx, views)
             try:
-                self.logits = _capture(graph, step)
+                self.logits = _capture(graph, lambda: model.forward(ctx, views))
             finally:
                 self.capturing = False
             self.graph = graph

@@ -49,13 +49,6 @@ class CudaOps:
         self.launches = 0
         self.lib.rv_last_error.restype = ctypes.c_char_p
         self.lib.rv_paged_attention_decode_scratch_bytes.restype = c_longlong
-        self.lib.rv_step_program_create.restype = c_void_p
-        for name in ("destroy", "len", "add_gemm", "add_resid", "add_conv", "add_qk", "add_swiglu",
-                     "add_logits", "finish", "run", "reset"):
-            fn = getattr(self.lib, "rv_step_program_" + name)
-            if name == "destroy":
-                fn.restype = None
-                fn.argtypes = [c_void_p]
         self._scratch = {}
         self._retired = []
         self._attn_libs = {}

@@ -105,26 +105,4 @@ class Attention(Mixer):
         return self.ops.linear(out, self.w_out, out_dtype=self.dtype)
 
 
-    def emit(self, program, rows, ctx, cache):
-        s = self.spec
-        if (self.w_qkv.dtype != torch.bfloat16 or not cache.owns or not self.has_kv
-                or s.head_dim % 2 or s.head_dim > 256 or s.hidden % 8
-                or (s.num_heads * s.head_dim) % 8 or cache.k.dtype != torch.bfloat16):
-            return None
-        group = ctx.groups[cache.group]
-        q = program.qk(program.gemm(rows, self.w_qkv), s.num_heads, s.num_kv_heads, s.head_dim,
-                       self.q_norm, self.k_norm, s.qk_norm.eps if s.qk_norm else 0.0,
-                       self.position.rotation_table(), ctx.positions, group.slot_mapping,
-                       cache.k, cache.v)
-        out = None
-        if not program.dry:
-            out = program.buffer(s.num_heads * s.head_dim)
-            ops, scale = self.ops, self.scale
-            program.call(lambda: ops.paged_attention(
-                q, s.num_heads, s.num_kv_heads, s.head_dim, cache.k, cache.v, ctx, group, scale,
-                s.window, out))
-        return program.gemm(program.rows_from(out) if out is not None
-                            else program.rows_from_width(s.num_heads * s.head_dim), self.w_out)
-
-
 register_mixer("attention", Attention)

@@ -63,13 +63,6 @@ class Mixer:
     def forward(self, normed, ctx, cache):
         raise NotImplementedError
 
-    def emit(self, program, rows, ctx, cache):
-        """Describe this mixer's share of a single-token step to a `StepProgram`
-        (`rvllm_b200.kernels.program`): takes the normed `Rows`, returns the `Sums` of its
-        output product.  None (the default): this mixer has no such description, and steps of
-        a model that holds it run kernel by kernel through `forward`."""
-        return None
-
 
 class FeedForward:
     """feed_forward(normed[N, hidden], ctx) -> [N, hidden]"""
@@ -83,10 +76,6 @@ class FeedForward:
 
     def forward(self, normed, ctx):
         raise NotImplementedError
-
-    def emit(self, program, rows, ctx):
-        """As `Mixer.emit`: `Rows` in, the `Sums` of the output product out, or None."""
-        return None
 
 
 class Norm:
@@ -109,11 +98,6 @@ class Norm:
         """The normalised rows of `x` (compute dtype), with no residual stream involved:
         what a norm placed after a sub-layer applies to its output."""
         raise NotImplementedError
-
-    def emit_add_norm(self, program, pending):
-        """As `Mixer.emit`: the stream takes `pending` (the model's `Embedding` or a
-        sub-layer's `Sums`); returns the normed `Rows`, or None."""
-        return None
 
 
 class PositionEncoding:
@@ -148,11 +132,6 @@ class Arrangement:
 
     def forward(self, stream, ctx, cache):
         raise NotImplementedError
-
-    def emit(self, program, pending, ctx, cache):
-        """As `Mixer.emit` for a whole block: `pending` is what the stream has not taken in
-        yet; returns the block's own pending `Sums`, or None."""
-        return None
 
 
 @dataclass

@@ -76,13 +76,4 @@ class PreNormBlock(Arrangement):
         return Stream(stream.resid, out)
 
 
-    def emit(self, program, pending, ctx, cache):
-        if self.post_mixer is not None or self.post_ffn is not None:
-            return None
-        rows = self.mixer_norm.emit_add_norm(program, pending)
-        mixed = self.mixer.emit(program, rows, ctx, cache) if rows is not None else None
-        rows2 = self.ffn_norm.emit_add_norm(program, mixed) if mixed is not None else None
-        return self.feed_forward.emit(program, rows2, ctx) if rows2 is not None else None
-
-
 register_arrangement("pre_norm", PreNormBlock)

@@ -41,11 +41,4 @@ class SwiGLU(FeedForward):
         return self.ops.linear(act, self.down, out_dtype=self.dtype)
 
 
-    def emit(self, program, rows, ctx):
-        if self.gate_up.dtype != torch.bfloat16 or self.spec.ffn_dim % 8 or self.spec.hidden % 8:
-            return None
-        act = program.swiglu(program.gemm(rows, self.gate_up), self.spec.ffn_dim)
-        return program.gemm(act, self.down)
-
-
 register_feed_forward("swiglu", SwiGLU)

@@ -86,32 +86,6 @@ class Model:
                          else mixer_class(m.kind).cache_need(m))
         return needs
 
-    def build_program(self, ctx, caches):
-        """A `StepProgram` for steps shaped like `ctx` (single tokens only, index arrays at
-        fixed addresses), or None when the kernel set has no step programs, the step does not
-        fit one, or a part of the model cannot describe itself to one."""
-        from ..kernels import program as sp
-        if (not sp.enabled() or not hasattr(self.ops, "lib") or self.dtype != torch.bfloat16
-                or ctx.n_decode != ctx.n_tokens or not 1 <= ctx.n_tokens <= sp.TOKENS
-                or self.spec.hidden % 8 or self.embedding.dtype != torch.bfloat16
-                or self.head.dtype != torch.bfloat16 or ctx.logit_rows.shape[0] != ctx.n_tokens):
-            return None
-        prog = sp.StepProgram(self.ops, self.device, ctx.n_tokens, self.spec.hidden)
-        for dry in (True, False):
-            prog.begin(dry)
-            pending = sp.Embedding(self.embedding, 1.0 if self.spec.embedding_scale is None
-                                   else float(self.spec.embedding_scale), ctx.token_ids)
-            for call, cache in zip(self.spec.order, caches):
-                pending = self.blocks[call.layer].emit(prog, pending, ctx, cache)
-                if pending is None:
-                    return None
-            rows = self.final_norm.emit_add_norm(prog, pending)
-            if rows is None:
-                return None
-            prog.logits(prog.gemm(rows, self.head))
-        prog.finish()
-        return prog
-
     def forward(self, ctx, caches) -> torch.Tensor:
         """Run the step's tokens; float32 logits [len(ctx.logit_rows), vocab]."""
         n = ctx.n_tokens

@@ -34,9 +34,6 @@ class RMSNorm(Norm):
         return out
 
 
-    def emit_add_norm(self, program, pending):
-        return program.add_norm(pending, self.weight, self.spec.eps)
-
     def norm(self, x, ctx):
         out = torch.empty((x.shape[0], self.spec.size), dtype=self.dtype, device=x.device)
         self.ops.add_rmsnorm(None, x, self.weight, self.spec.eps, out, None)

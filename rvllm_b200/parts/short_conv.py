@@ -79,16 +79,4 @@ class ShortConv(Mixer):
         return out
 
 
-    def emit(self, program, rows, ctx, cache):
-        if self.w_in.dtype != torch.bfloat16 or self.spec.hidden % 8 or self.spec.taps > 8:
-            return None
-        if cache is not None and not cache.owns:
-            return None
-        y = program.conv(program.gemm(rows, self.w_in), self.filter, self.b_in, self.b_conv,
-                         cache.state if cache is not None else None, ctx)
-        out = program.gemm(y, self.w_out)
-        out.bias = self.b_out
-        return out
-
-
 register_mixer("short_conv", ShortConv)
