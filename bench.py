@@ -504,7 +504,7 @@ def run_kernels(args):
         out[f"attn_prefill_t{T}"] = {"us": round(us, 1), "TFLOP/s": round(flops / us / 1e6, 1),
                                      "frac_bf16": round(flops / us / 1e6 / pk["bf16_tflops"], 3)}
     if args.kernel == "all" or args.kernel.startswith("gemm"):
-        M = 8
+        M = args.kernel_m
         x = torch.randn(M, 8192, device="cuda", dtype=torch.bfloat16)
         shapes = ((6144, 2048), (2048, 2048), (3072, 2048), (16384, 2048), (2048, 8192),
                   (65536, 2048))
@@ -646,6 +646,7 @@ def main():
     ap.add_argument("--kernel", default="all",
                     help="with --only kernels: attn_decode, attn_prefill, gemm, gemm:NxK, copy_rate or all")
     ap.add_argument("--kernel-batch", type=int, default=64)
+    ap.add_argument("--kernel-m", type=int, default=8, help="tokens of the gemm micro-benchmark")
     ap.add_argument("--kernel-ctx", type=int, default=4096)
     args = ap.parse_args()
     if args.impl == "reference":

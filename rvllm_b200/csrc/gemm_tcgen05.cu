@@ -331,9 +331,13 @@ extern "C" int rv_gemm_tcgen05_splits(int N, int K) {
 // rings that leave room for one block per SM measured much slower.
 static int pick_stages(int n_pad) {
     static int want = env_int("RVLLM_GEMM_STAGES", 6);
+    static int want_wide = env_int("RVLLM_GEMM_STAGES_WIDE", 4);
     const int per_stage = RV_GEMM_BM * RV_GEMM_BK * 2 + n_pad * RV_GEMM_BK * 2;
     int st = (RV_GEMM_SMEM_LIMIT - 1024) / per_stage;
-    if (st > want) st = want;
+    // More than 16 tokens: stages are larger, and four of them keep two blocks on an SM (a
+    // deeper ring copies no faster: an SM's copy rate does not grow beyond four stages)
+    const int cap = n_pad > 16 ? want_wide : want;
+    if (st > cap) st = cap;
     return st > RV_GEMM_MAX_STAGES ? RV_GEMM_MAX_STAGES : st;
 }
 

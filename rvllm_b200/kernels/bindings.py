@@ -210,7 +210,7 @@ class CudaOps:
         if (self.fuse_qkv_rope and k_cache is not None and num_kv_heads > 0 and head_dim == 64
                 and out_dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16
                 and w_qkv.shape[0] == (num_heads + 2 * num_kv_heads) * 64
-                and self._small_product(x, w_qkv, out_dtype)):
+                and x.shape[0] <= 16 and self._small_product(x, w_qkv, out_dtype)):
             m, k = x.shape
             n = w_qkv.shape[0]
             qkv = torch.empty((m, n), dtype=out_dtype, device=x.device)
