@@ -620,6 +620,114 @@ def run_workload(name, verbose=False):
     return result
 
 
+def run_further(args):
+    """Speed at further sizes, one JSON line: decode at batch 8 with 16,384 and 32,768 tokens of
+    context, a prompt of 8,192 tokens taken in portions of 2,048 (convolution state and attention
+    across portion boundaries at the real widths), and the samplers over 65,536 logits."""
+    import torch
+
+    from rvllm_b200.config import architecture, config_from_dict
+    from rvllm_b200.engine import ModelRunner, StepEntry, graphs_default, load_model, make_cache
+    from rvllm_b200.parts.model import param_decls
+    from rvllm_b200.weights import write_random_model
+
+    pk = peaks()
+    data = dict(LFM2_1_2B)
+    data["max_position_embeddings"] = 32768
+    cfg = config_from_dict(data)
+    tmp = tempfile.mkdtemp(prefix="rvllm_bench_")
+    try:
+        folder = write_random_model(os.path.join(tmp, "model"), cfg, seed=0)
+        model, cfg = load_model(folder, "bfloat16", "cuda")
+    finally:
+        shutil.rmtree(tmp, ignore_errors=True)
+    ops = model.ops
+    spec = architecture(cfg.architecture).build_spec(cfg)
+    weight_bytes, matmul_params = model_bytes_and_flops(cfg, param_decls(spec))
+    n_attn = len(cfg.full_attn_idxs)
+    kv_per_token = n_attn * 2 * cfg.num_key_value_heads * cfg.head_dim * 2
+    gen = torch.Generator().manual_seed(0)
+    out = {"only": "further", "peaks": pk["source"]}
+
+    def ids(n):
+        return torch.randint(0, cfg.vocab_size, (n,), generator=gen).tolist()
+
+    B, steps = 8, 128
+    for ctx in (16384, 32768):
+        cache = make_cache(model, PAGE, B * (ctx // PAGE), B)
+        runner = ModelRunner(model, cache, ops, use_graphs=graphs_default())
+        for i in range(B):
+            runner.add_request(i)
+            toks = ids(ctx - steps - 8)
+            for a in range(0, len(toks), 2048):
+                runner.step([StepEntry(i, toks[a:a + 2048], ())])
+        first = runner.decode_greedy(list(range(B)), [1] * B, 8)[-1].tolist()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        runner.decode_greedy(list(range(B)), first, steps)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        nbytes = weight_bytes + B * (ctx - steps / 2) * kv_per_token
+        out[f"decode_b{B}_ctx{ctx}"] = {"tok_s": round(B / (ms / 1e3), 1), "ms_per_step": round(ms, 4),
+                                         "frac_hbm": round(nbytes / (ms / 1e3) / 1e9 / pk["hbm_gbs"], 4)}
+        del runner, cache
+
+    # a prompt of 8,192 tokens in portions of 2,048
+    T, portion = 8192, 2048
+    cache = make_cache(model, PAGE, T // PAGE, 1)
+    runner = ModelRunner(model, cache, ops, use_graphs=False)
+    toks = ids(T)
+    times = []
+    for it in range(4):
+        runner.add_request("p")
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for a in range(0, T, portion):
+            runner.step([StepEntry("p", toks[a:a + portion], (portion - 1,) if a + portion == T else ())])
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+        runner.end_request("p")
+    ms = sorted(times[1:])[1]
+    flops = 2.0 * T * matmul_params + 2.0 * cfg.vocab_size * cfg.hidden_size \
+        + n_attn * 4.0 * cfg.num_attention_heads * cfg.head_dim * T * (T + 1) / 2
+    out["prefill_8192_in_portions_of_2048"] = {
+        "tok_s": round(T / (ms / 1e3), 1), "ms": round(ms, 3),
+        "frac_bf16": round(flops / (ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
+    del runner, cache
+
+    # the samplers over [rows, 65,536] float32 logits
+    for rows in (8, 64):
+        logits = torch.randn(rows, cfg.vocab_size, device="cuda", generator=None) * 3
+        temp = torch.full((rows,), 0.8, device="cuda")
+        seed = torch.arange(rows, dtype=torch.int64, device="cuda")
+        counter = torch.zeros(rows, dtype=torch.int64, device="cuda")
+
+        def timed(fn, reps=20):
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            return round(e0.elapsed_time(e1) * 1e3 / reps, 1)
+        entry = {"argmax_us": timed(lambda: ops.argmax(logits))}
+        for top_p in (1.0, 0.9):
+            tp = torch.full((rows,), top_p, device="cuda")
+            entry[f"sample_top_p_{top_p}_us"] = timed(lambda: ops.sample(logits, temp, tp, seed, counter))
+        entry["logits_MB"] = round(rows * cfg.vocab_size * 4 / 1e6, 1)
+        out[f"sampling_rows{rows}"] = entry
+    ops.check_status()
+    print(json.dumps(out))
+    return 0
+
+
 def run_reference(args):
     print(json.dumps({
         "impl": "reference",
@@ -637,7 +745,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--size", default="1.2b", choices=sorted(SIZES),
                     help="layer sizes: LFM2-1.2B (the default and the headline), 700M or 350M")
-    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "kernels", "breakdown", "workload"],
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "kernels", "breakdown", "workload", "further"],
                     help="run one part only (for profiling); the JSON line then lacks the rest")
     ap.add_argument("--workloads", default="both", choices=["both", "none"] + sorted(WORKLOADS),
                     help="scheduler workloads to add to the line (default: both)")
@@ -658,6 +766,8 @@ def main():
         args.warmup = 3
     if args.only == "kernels":
         return run_kernels(args)
+    if args.only == "further":
+        return run_further(args)
     if args.only == "workload":
         print(json.dumps({"only": "workload", args.workload: run_workload(args.workload)}))
         return 0

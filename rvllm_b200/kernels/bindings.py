@@ -535,11 +535,9 @@ class CudaOps:
         self._need(top_p, "top-p values", torch.float32)
         self._need(seed, "seeds", torch.int64)
         self._need(counter, "counters", torch.int64)
-        greedy = self.argmax(logits)
         out = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
-        positive = temperature.clamp_min(1e-6)
-        self._check(self.lib.rv_sample(_ptr(logits), _ptr(positive),
+        self._check(self.lib.rv_sample(_ptr(logits), _ptr(temperature),
                                        _ptr(top_p), _ptr(seed), _ptr(counter), _ptr(out),
                                        c_int(logits.shape[0]), c_int(logits.shape[1]),
                                        self._stream()), "sample")
-        return torch.where(temperature > 0, out, greedy)
+        return out

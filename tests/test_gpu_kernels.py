@@ -444,6 +444,38 @@ def test_sample_matches_definition(ops, top_p):
     assert int(out[5]) == int(torch.argmax(logits[5]))
 
 
+@pytest.mark.parametrize("vocab", [1003, 20000, 65536, 73728, 80000])
+def test_sample_on_chip_and_from_memory(ops, vocab):
+    """The kernel that keeps a row's probabilities in registers and shared memory and the one
+    that re-reads the logits in every pass: rows that fit registers alone, registers and
+    shared memory, a row that fills the first kernel to its limit, and (80,000) rows too long
+    for it, which then is not used.  They add in different orders, so a draw within float32
+    rounding of a boundary may go to the neighbouring kept token: at most one row in twelve may
+    differ, and both must follow the definition (float64) with the same allowance."""
+    g = torch.Generator().manual_seed(vocab)
+    rows = 12
+    logits = (torch.randn(rows, vocab, generator=g) * 4)
+    temp = 0.5 + torch.rand(rows, generator=g)
+    temp[7] = 0.0                                   # a greedy row
+    tp = torch.tensor([1.0, 0.95, 0.9, 0.5, 0.3, 0.05] * 2)
+    seed = torch.arange(rows, dtype=torch.int64) * 13 + 1
+    counter = torch.arange(rows, dtype=torch.int64)
+    outs = []
+    try:
+        for mode in (1, 0):
+            ops.lib.rv_sample_set_onchip(mode)
+            outs.append(ops.sample(logits.cuda(), temp.cuda(), tp.cuda(), seed.cuda(),
+                                   counter.cuda()).cpu())
+    finally:
+        ops.lib.rv_sample_set_onchip(1)
+    assert int((outs[0] != outs[1]).sum()) <= 1
+    want = torch.tensor([sample_row(logits[m], float(temp[m]), float(tp[m]), int(seed[m]),
+                                    int(counter[m])) for m in range(rows)], dtype=torch.int32)
+    for got in outs:
+        assert int((got != want).sum()) <= 1, (got.tolist(), want.tolist())
+        assert int(got[7]) == int(torch.argmax(logits[7]))
+
+
 def test_sample_frequencies(ops):
     """Draws over many counters follow softmax(logits / T)."""
     logits = torch.tensor([[2.0, 1.0, 0.0, -1.0, 0.5]])
