@@ -88,12 +88,14 @@ class BatchBuilder:
         return self._host, self._dev
 
     def build(self, entries: Sequence[StepEntry], pad_reqs: int = 0,
-              pad_blocks: int = 0, buffers=None) -> StepContext:
+              pad_blocks: int = 0, buffers=None, row_order: Optional[Sequence[int]] = None
+              ) -> StepContext:
         """`entries` must already be ordered single-token requests first.  `pad_reqs` /
         `pad_blocks` pad the request count (with empty requests that every kernel
         skips) and the block-table width, so that a captured launch sequence sees the
         same addresses and sizes; `buffers` = (host, device) to fill instead of the
-        builder's own."""
+        builder's own.  `row_order`: the entries' indices in the order in which their wanted
+        rows are to come out (the callers' order, when the entries were reordered)."""
         cache = self.cache
         ps = cache.page_size
         q_lens = [len(e.tokens) for e in entries]
@@ -179,7 +181,9 @@ class BatchBuilder:
         k = 0
         if pad_reqs:
             rows[:] = np.arange(N)
-        for i, e in enumerate(entries if not pad_reqs else ()):
+        emit = range(len(entries)) if row_order is None else row_order
+        for i in (emit if not pad_reqs else ()):
+            e = entries[i]
             for w in e.want:
                 if not 0 <= w < q_lens[i]:
                     raise ValueError(f"request {e.req!r}: wanted place {w} is outside "

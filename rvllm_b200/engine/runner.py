@@ -107,19 +107,9 @@ class ModelRunner:
                 raise ValueError("device-fed tokens are for single-token entries only")
             logits = self._run(ordered, device_tokens)
         elif order != list(range(len(entries))):
-            logits = self._run(ordered)
-            # rows come out in `ordered` order; put them back in the callers' order
-            counts = [len(e.want) for e in ordered]
-            starts = [0]
-            for c in counts:
-                starts.append(starts[-1] + c)
-            perm = []
+            # the wanted rows come out in the callers' order: the row list is written that way
             where = {oi: k for k, oi in enumerate(order)}
-            for i in range(len(entries)):
-                k = where[i]
-                perm.extend(range(starts[k], starts[k + 1]))
-            if perm != list(range(len(perm))):
-                logits = logits[torch.tensor(perm, device=logits.device, dtype=torch.long)]
+            logits = self._run(ordered, row_order=[where[i] for i in range(len(entries))])
         else:
             logits = self._run(ordered)
         for e, total in zip(entries, totals):
@@ -127,19 +117,19 @@ class ModelRunner:
         self.steps += 1
         return logits
 
-    def _run(self, ordered: List[StepEntry], device_tokens=None) -> torch.Tensor:
+    def _run(self, ordered: List[StepEntry], device_tokens=None, row_order=None) -> torch.Tensor:
         if self.use_graphs and all(len(e.tokens) == 1 for e in ordered):
             return self._run_graph(ordered, device_tokens)
         if self.use_graphs and device_tokens is None:
-            logits = self._run_repeated_shape(ordered)
+            logits = self._run_repeated_shape(ordered, row_order)
             if logits is not None:
                 return logits
-        ctx = self.builder.build(ordered)
+        ctx = self.builder.build(ordered, row_order=row_order)
         if device_tokens is not None:
             ctx.token_ids[:len(ordered)].copy_(device_tokens)
         return self.model.forward(ctx, self.cache.views())
 
-    def _run_repeated_shape(self, ordered: List[StepEntry]) -> Optional[torch.Tensor]:
+    def _run_repeated_shape(self, ordered: List[StepEntry], row_order=None) -> Optional[torch.Tensor]:
         """Steps with prompt portions: the second time the same shape comes (the same token
         counts, wanted places and block-table width, as with a fixed portion size), its launch
         sequence is captured, and from then on replayed.  Returns None when this step has to
@@ -149,7 +139,7 @@ class ModelRunner:
         blocks = -(-ctx_max // ps)
         block_bucket = max(16, 1 << (blocks - 1).bit_length())
         key = (tuple(len(e.tokens) for e in ordered), tuple(tuple(e.want) for e in ordered),
-               block_bucket)
+               block_bucket, tuple(row_order) if row_order is not None else None)
         g = self._shape_graphs.get(key)
         if g is None:
             if key not in self._seen_shapes:
@@ -164,7 +154,7 @@ class ModelRunner:
         if g.broken:
             return None
         try:
-            logits = g.run(ordered)
+            logits = g.run(ordered, row_order)
         except RuntimeError as e:
             if g.graph is not None and not g.capturing:
                 raise
@@ -350,10 +340,10 @@ class _ShapeGraph:
         self.capturing = False
         self.kernels_per_replay = 0
 
-    def run(self, entries) -> torch.Tensor:
+    def run(self, entries, row_order=None) -> torch.Tensor:
         runner = self.runner
         ctx = runner.builder.build(entries, pad_blocks=self.block_bucket,
-                                   buffers=(self.host, self.dev))
+                                   buffers=(self.host, self.dev), row_order=row_order)
         ctx.max_ctx_len = self.block_bucket * runner.cache.page_size
         if self.graph is None:
             launches = runner.model.ops.launches
