@@ -441,14 +441,18 @@ def run_kernels(args):
         rows = sms * iters * 16384 // (K * 2) + 128
         w = torch.randn(rows, K, device="cuda", dtype=torch.bfloat16)      # 1.2 GB: larger than L2
         status = ops.status_word("cuda")
-        for mode, name in ((0, "box"), (1, "bulk")):
+        for mode, name, chunk in ((0, "box", 16384), (1, "bulk", 16384), (1, "bulk32k", 32768),
+                                  (1, "bulk64k", 65536)):
             for grid in (sms, sms // 4, 1):
-                for stages in (4, 10):
+                for stages in (3, 4, 10):
+                    if stages * chunk > 200 * 1024:
+                        continue
+
                     def call():
                         ops._check(ops.lib.rv_copy_probe(
                             ctypes.c_void_p(w.data_ptr()), ctypes.c_longlong(rows), ctypes.c_int(K),
-                            ctypes.c_int(mode), ctypes.c_int(grid), ctypes.c_int(iters),
-                            ctypes.c_int(stages), ctypes.c_void_p(status.data_ptr()),
+                            ctypes.c_int(mode), ctypes.c_int(grid), ctypes.c_int(iters * 16384 // chunk),
+                            ctypes.c_int(stages), ctypes.c_int(chunk), ctypes.c_void_p(status.data_ptr()),
                             ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)), "copy_probe")
                     call()
                     torch.cuda.synchronize()
@@ -457,7 +461,7 @@ def run_kernels(args):
                     call()
                     e1.record()
                     torch.cuda.synchronize()
-                    gbs = grid * iters * 16384 / (e0.elapsed_time(e1) * 1e-3) / 1e9
+                    gbs = grid * (iters * 16384 // chunk) * chunk / (e0.elapsed_time(e1) * 1e-3) / 1e9
                     out[f"copy_{name}_sms{grid}_stages{stages}"] = {
                         "GB/s": round(gbs, 1), "GB/s_per_sm": round(gbs / grid, 1)}
         ops.check_status()

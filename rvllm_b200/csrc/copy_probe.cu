@@ -9,15 +9,9 @@
 // 148 SMs, where HBM is the limit).  `bench.py --only kernels --kernel copy_rate` runs it.
 #include "tcgen05_common.cuh"
 
-__device__ __forceinline__ void probe_bulk_1d(void* dst, const void* src, unsigned bytes,
-                                              unsigned long long* bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
-}
-
 __global__ void __launch_bounds__(64, 1)
 copy_probe_kernel(const __grid_constant__ CUtensorMap map, const char* flat, int mode, int iters,
-                  int stages, int kblocks, int* status) {
+                  int stages, int kblocks, int chunk, int* status) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* ring = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     __shared__ unsigned long long full[16];
@@ -37,31 +31,35 @@ copy_probe_kernel(const __grid_constant__ CUtensorMap map, const char* flat, int
             return;
         }
         if (i < iters) {
-            mbar_expect_tx(&full[s], 16384);
+            mbar_expect_tx(&full[s], (unsigned)chunk);
             const long long item = (long long)blockIdx.x * iters + i;
             if (mode == 0)
-                tma_load_2d(ring + s * 16384, &map, &full[s], (int)(item % kblocks) * 64,
+                tma_load_2d(ring + (size_t)s * chunk, &map, &full[s], (int)(item % kblocks) * 64,
                             (int)(item / kblocks) * 128);
             else
-                probe_bulk_1d(ring + s * 16384, flat + item * 16384, 16384, &full[s]);
+                bulk_load_1d(ring + (size_t)s * chunk, flat + item * chunk, (unsigned)chunk, &full[s]);
         }
     }
 }
 
 // `w`: [rows, K] bfloat16 with rows * K * 2 >= grid * iters * 16384 bytes.
+// `chunk`: bytes per copy (16384 for boxes; for bulk copies any multiple of 16 up to 65536).
 extern "C" int rv_copy_probe(const void* w, long long rows, int K, int mode, int grid, int iters,
-                             int stages, int* status, void* stream) {
+                             int stages, int chunk, int* status, void* stream) {
     if (K % 64 || stages < 1 || stages > 12 || grid < 1 || iters < 1 || (mode != 0 && mode != 1))
         RV_FAIL("copy_probe: bad arguments");
-    if ((long long)grid * iters * 16384 > rows * K * 2) RV_FAIL("copy_probe: the matrix is too small");
+    if (chunk % 16 || chunk < 16 || chunk > 65536 || (mode == 0 && chunk != 16384) ||
+        (size_t)stages * chunk > 200 * 1024)
+        RV_FAIL("copy_probe: bad chunk size %d", chunk);
+    if ((long long)grid * iters * chunk > rows * K * 2) RV_FAIL("copy_probe: the matrix is too small");
     CUtensorMap map;
     if (make_map(&map, w, rows, K, 128)) return 1;
-    const size_t smem = (size_t)stages * 16384 + 1024;
+    const size_t smem = (size_t)stages * chunk + 1024;
     cudaError_t e = cudaFuncSetAttribute(copy_probe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)smem);
     if (e != cudaSuccess) RV_FAIL("copy_probe: %s", cudaGetErrorString(e));
     copy_probe_kernel<<<grid, 64, smem, (cudaStream_t)stream>>>(map, (const char*)w, mode, iters, stages,
-                                                                K / 64, status);
+                                                                K / 64, chunk, status);
     RV_CHECK_LAUNCH("copy_probe");
     return 0;
 }

@@ -73,16 +73,20 @@ struct RvQkvEpilogue {
 // query and key head is RMS-normalised and rotated, queries go to `out`, keys and values to
 // their slots of the paged cache: the separate kernel for that, and its place in the chain of
 // dependent launches, are gone.
-template <typename TO, bool QKV>
+template <typename TO, bool QKV, int KBS>
 __global__ void __launch_bounds__(128) gemm_tcgen05_kernel(
     const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
     TO* __restrict__ out, int* __restrict__ status, int M, int N, int kblocks, int n_pad,
-    int stages, const RvQkvEpilogue epi) {
+    int stages, const RvQkvEpilogue epi, const bf16* __restrict__ w_tiled) {
+    constexpr int kbs = KBS;          // K blocks of 64 per stage
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // the dynamic segment is aligned by hand: swizzled tiles need 1024-byte alignment
     unsigned char* base = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    const int w_bytes = RV_GEMM_BM * RV_GEMM_BK * 2;
-    const int x_bytes = n_pad * RV_GEMM_BK * 2;
+    // a stage holds `kbs` K blocks of 64: kbs weight tiles of 16 KB (one contiguous copy when
+    // the matrix is laid out tile by tile) and kbs x tiles
+    const int w_tile = RV_GEMM_BM * RV_GEMM_BK * 2, x_tile = n_pad * RV_GEMM_BK * 2;
+    const int w_bytes = kbs * w_tile;
+    const int x_bytes = kbs * x_tile;
     unsigned char* w_tiles = base;
     unsigned char* x_tiles = base + stages * w_bytes;
     __shared__ __align__(8) unsigned long long full_bar[RV_GEMM_MAX_STAGES];
@@ -99,6 +103,7 @@ __global__ void __launch_bounds__(128) gemm_tcgen05_kernel(
     const int kb0 = (int)((long long)kblocks * split / splits);
     const int kb1 = (int)((long long)kblocks * (split + 1) / splits);
     const int nkb = kb1 - kb0;
+    const int nst = (nkb + kbs - 1) / kbs;             // stages' worth of work
     unsigned tmem_cols = 32;
     while ((int)tmem_cols < n_pad) tmem_cols <<= 1;
 
@@ -124,20 +129,41 @@ __global__ void __launch_bounds__(128) gemm_tcgen05_kernel(
 
     if (warp == 0 && lane == 0) {
         // ---- producer: TMA copies of W and x tiles ------------------------------------
-        const unsigned tx = (unsigned)(w_bytes + x_bytes);
+        // The weight tiles of a stage come as one contiguous bulk copy when the matrix was laid
+        // out tile by tile beforehand (`rv_gemm_tile_weights`; an SM copies 32 KB at a time more
+        // than twice as fast as tensor-map boxes of 128 strided rows), else as tensor-map boxes.
+        auto blocks_of = [&](int i) { return min(kbs, nkb - i * kbs); };
+        auto load_w = [&](int s, int i) {
+            const int kb = kb0 + i * kbs, cnt = blocks_of(i);
+            mbar_expect_tx(&full_bar[s], (unsigned)(cnt * (w_tile + x_tile)));
+            if (w_tiled) {
+                bulk_load_1d(w_tiles + s * w_bytes,
+                             w_tiled + ((size_t)tile * kblocks + kb) * (RV_GEMM_BM * RV_GEMM_BK),
+                             (unsigned)(cnt * w_tile), &full_bar[s]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < kbs; ++j)
+                    if (j < cnt)
+                        tma_load_2d(w_tiles + s * w_bytes + j * w_tile, &map_w, &full_bar[s],
+                                    (kb + j) * RV_GEMM_BK, tile * RV_GEMM_BM);
+            }
+        };
+        auto load_x = [&](int s, int i) {
+            const int kb = kb0 + i * kbs, cnt = blocks_of(i);
+#pragma unroll
+            for (int j = 0; j < kbs; ++j)
+                if (j < cnt)
+                    tma_load_2d(x_tiles + s * x_bytes + j * x_tile, &map_x, &full_bar[s],
+                                (kb + j) * RV_GEMM_BK, 0);
+        };
         // fill the ring with weight tiles before waiting for the previous kernel: they
         // stream from HBM while it is still running
-        const int pre = min(nkb, stages);
-        for (int i = 0; i < pre; ++i) {
-            mbar_expect_tx(&full_bar[i], tx);
-            tma_load_2d(w_tiles + i * w_bytes, &map_w, &full_bar[i], (kb0 + i) * RV_GEMM_BK,
-                        tile * RV_GEMM_BM);
-        }
+        const int pre = min(nst, stages);
+        for (int i = 0; i < pre; ++i) load_w(i, i);
         rv_pdl_wait();
-        for (int i = 0; i < pre; ++i)
-            tma_load_2d(x_tiles + i * x_bytes, &map_x, &full_bar[i], (kb0 + i) * RV_GEMM_BK, 0);
+        for (int i = 0; i < pre; ++i) load_x(i, i);
         int issued = pre;
-        for (int i = pre; i < nkb; ++i) {
+        for (int i = pre; i < nst; ++i) {
             const int s = i % stages;
             {
                 const unsigned parity = ((i / stages) - 1) & 1;
@@ -146,10 +172,8 @@ __global__ void __launch_bounds__(128) gemm_tcgen05_kernel(
                     break;
                 }
             }
-            mbar_expect_tx(&full_bar[s], tx);
-            tma_load_2d(w_tiles + s * w_bytes, &map_w, &full_bar[s], (kb0 + i) * RV_GEMM_BK,
-                        tile * RV_GEMM_BM);
-            tma_load_2d(x_tiles + s * x_bytes, &map_x, &full_bar[s], (kb0 + i) * RV_GEMM_BK, 0);
+            load_w(s, i);
+            load_x(s, i);
             issued = i + 1;
         }
         // no copy of this block may still be in flight when it returns
@@ -167,18 +191,23 @@ __global__ void __launch_bounds__(128) gemm_tcgen05_kernel(
         // instruction descriptor: D float32, A and B bfloat16, both K-major, N = n_pad, M = 128
         const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) |
                                ((unsigned)(n_pad >> 3) << 17) | ((unsigned)(RV_GEMM_BM >> 4) << 24);
-        for (int i = 0; i < nkb; ++i) {
+        for (int i = 0; i < nst; ++i) {
             const int s = i % stages;
             if (!mbar_wait(&full_bar[s], (i / stages) & 1, &failed)) {
                 if (!failed) { failed = 1; atomicCAS(status, 0, 3); }
                 break;
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const unsigned long long a0 = smem_desc_sw128(w_tiles + s * w_bytes);
-            const unsigned long long b0 = smem_desc_sw128(x_tiles + s * x_bytes);
+            const int cnt = min(kbs, nkb - i * kbs);
 #pragma unroll
-            for (int k = 0; k < RV_GEMM_BK / 16; ++k)      // 32 bytes per K = 16 step
-                tcgen05_mma_f16(tmem_base, a0 + 2 * k, b0 + 2 * k, idesc, (i | k) != 0);
+            for (int j = 0; j < kbs; ++j) {
+                if (j >= cnt) break;
+                const unsigned long long a0 = smem_desc_sw128(w_tiles + s * w_bytes + j * w_tile);
+                const unsigned long long b0 = smem_desc_sw128(x_tiles + s * x_bytes + j * x_tile);
+#pragma unroll
+                for (int k = 0; k < RV_GEMM_BK / 16; ++k)      // 32 bytes per K = 16 step
+                    tcgen05_mma_f16(tmem_base, a0 + 2 * k, b0 + 2 * k, idesc, (i | j | k) != 0);
+            }
             tcgen05_commit(&empty_bar[s]);                  // frees the stage when the MMAs are done
         }
         tcgen05_commit(&accum_bar);                         // arrives when every MMA above is done
@@ -329,10 +358,11 @@ extern "C" int rv_gemm_tcgen05_splits(int N, int K) {
 // Stages of the copy ring.  Six by default (108 KB with 16 tokens): two blocks fit an SM, so
 // the next kernel's blocks can already fill their rings while this one computes; deeper
 // rings that leave room for one block per SM measured much slower.
-static int pick_stages(int n_pad) {
-    static int want = env_int("RVLLM_GEMM_STAGES", 6);
+static int pick_stages(int n_pad, int kbs) {
+    static int want1 = env_int("RVLLM_GEMM_STAGES", 6);
     static int want_wide = env_int("RVLLM_GEMM_STAGES_WIDE", 4);
-    const int per_stage = RV_GEMM_BM * RV_GEMM_BK * 2 + n_pad * RV_GEMM_BK * 2;
+    const int want = kbs > 1 ? (want1 + kbs - 1) / kbs : want1;      // the same ring in bytes
+    const int per_stage = kbs * (RV_GEMM_BM * RV_GEMM_BK * 2 + n_pad * RV_GEMM_BK * 2);
     int st = (RV_GEMM_SMEM_LIMIT - 1024) / per_stage;
     // More than 16 tokens: stages are larger, and four of them keep two blocks on an SM (a
     // deeper ring copies no faster: an SM's copy rate does not grow beyond four stages)
@@ -343,25 +373,31 @@ static int pick_stages(int n_pad) {
 
 // Once per process, outside any stream capture: raise the kernels' shared-memory limit and
 // look up the driver's tensor-map encoder.
+template <typename TO, bool QKV, int KBS>
+static cudaError_t raise_smem() {
+    return cudaFuncSetAttribute(gemm_tcgen05_kernel<TO, QKV, KBS>,
+                                cudaFuncAttributeMaxDynamicSharedMemorySize, RV_GEMM_SMEM_LIMIT);
+}
+
 extern "C" int rv_gemm_tcgen05_init() {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<bf16, false>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         RV_GEMM_SMEM_LIMIT);
-    if (e == cudaSuccess)
-        e = cudaFuncSetAttribute(gemm_tcgen05_kernel<float, false>,
-                                 cudaFuncAttributeMaxDynamicSharedMemorySize, RV_GEMM_SMEM_LIMIT);
-    if (e == cudaSuccess)
-        e = cudaFuncSetAttribute(gemm_tcgen05_kernel<bf16, true>,
-                                 cudaFuncAttributeMaxDynamicSharedMemorySize, RV_GEMM_SMEM_LIMIT);
+    cudaError_t e = raise_smem<bf16, false, 1>();
+    if (e == cudaSuccess) e = raise_smem<bf16, false, 2>();
+    if (e == cudaSuccess) e = raise_smem<bf16, false, 3>();
+    if (e == cudaSuccess) e = raise_smem<float, false, 1>();
+    if (e == cudaSuccess) e = raise_smem<float, false, 2>();
+    if (e == cudaSuccess) e = raise_smem<float, false, 3>();
+    if (e == cudaSuccess) e = raise_smem<bf16, true, 1>();
+    if (e == cudaSuccess) e = raise_smem<bf16, true, 2>();
+    if (e == cudaSuccess) e = raise_smem<bf16, true, 3>();
     if (e != cudaSuccess) RV_FAIL("gemm_tcgen05: %s", cudaGetErrorString(e));
     if (!encode_fn()) RV_FAIL("gemm_tcgen05: cuTensorMapEncodeTiled is not available in this driver");
     return 0;
 }
 
-template <typename TO, bool QKV>
-static int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, void* out, int* status, int M,
+template <typename TO, bool QKV, int KBS>
+static int launch_kbs(const CUtensorMap& map_w, const CUtensorMap& map_x, void* out, int* status, int M,
                   int N, int kblocks, int n_pad, int stages, int tiles, int splits, size_t smem,
-                  const RvQkvEpilogue& epi, cudaStream_t stream) {
+                  const RvQkvEpilogue& epi, const void* w_tiled, cudaStream_t stream) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(tiles, splits, 1);
     cfg.blockDim = dim3(128, 1, 1);
@@ -376,17 +412,31 @@ static int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, void* out,
     attr[1].val.programmaticStreamSerializationAllowed = rv_pdl_enabled();
     cfg.attrs = attr;
     cfg.numAttrs = 2;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<TO, QKV>, map_w, map_x, (TO*)out,
-                                       status, M, N, kblocks, n_pad, stages, epi);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<TO, QKV, KBS>, map_w, map_x, (TO*)out,
+                                       status, M, N, kblocks, n_pad, stages, epi, (const bf16*)w_tiled);
     if (e != cudaSuccess) RV_FAIL("gemm_tcgen05: %s", cudaGetErrorString(e));
     return 0;
+}
+
+template <typename TO, bool QKV>
+static int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, void* out, int* status, int M,
+                  int N, int kblocks, int n_pad, int stages, int tiles, int splits, size_t smem,
+                  const RvQkvEpilogue& epi, const void* w_tiled, int kbs, cudaStream_t stream) {
+    if (kbs == 3)
+        return launch_kbs<TO, QKV, 3>(map_w, map_x, out, status, M, N, kblocks, n_pad, stages, tiles,
+                                      splits, smem, epi, w_tiled, stream);
+    if (kbs == 2)
+        return launch_kbs<TO, QKV, 2>(map_w, map_x, out, status, M, N, kblocks, n_pad, stages, tiles,
+                                      splits, smem, epi, w_tiled, stream);
+    return launch_kbs<TO, QKV, 1>(map_w, map_x, out, status, M, N, kblocks, n_pad, stages, tiles,
+                                  splits, smem, epi, w_tiled, stream);
 }
 
 // y = x . W^T.  `status` is a device int the kernel sets to a non-zero code if a bounded
 // wait ran out (1: producer waiting for a free stage, 2: copies still in flight at exit,
 // 3: MMA issuer waiting for data, 4: epilogue waiting for the accumulator).
 static int gemm(const void* x, const void* w, void* out, int out_dtype, int* status, int M, int N,
-                int K, const RvQkvEpilogue* epi, void* stream) {
+                int K, const RvQkvEpilogue* epi, const void* w_tiled, void* stream) {
     if (M == 0) return 0;
     if (M < 0 || M > 256 || N <= 0 || K <= 0)
         RV_FAIL("gemm_tcgen05: sizes out of range (M = %d must be 1..256, N = %d, K = %d)", M, N, K);
@@ -396,8 +446,11 @@ static int gemm(const void* x, const void* w, void* out, int out_dtype, int* sta
     const int tiles = (N + RV_GEMM_BM - 1) / RV_GEMM_BM;
     const int kblocks = (K + RV_GEMM_BK - 1) / RV_GEMM_BK;
     const int splits = rv_gemm_tcgen05_splits(N, K);
-    const int stages = pick_stages(n_pad);
-    const size_t ring = (size_t)stages * (RV_GEMM_BM * RV_GEMM_BK * 2 + n_pad * RV_GEMM_BK * 2);
+    // K blocks per stage: two (copies of 32 KB) for a matrix laid out tile by tile and few tokens
+    static int kbs_tiled = env_int("RVLLM_GEMM_STAGE_BLOCKS", 2);
+    const int kbs = (w_tiled && n_pad <= 16 && (kbs_tiled == 2 || kbs_tiled == 3)) ? kbs_tiled : 1;
+    const int stages = pick_stages(n_pad, kbs);
+    const size_t ring = (size_t)stages * kbs * (RV_GEMM_BM * RV_GEMM_BK * 2 + n_pad * RV_GEMM_BK * 2);
     if (stages < 2) RV_FAIL("gemm_tcgen05: no room for two stages with %d tokens", M);
     if (splits > 1 && (size_t)M * RV_GEMM_BM * 4 > ring)
         RV_FAIL("gemm_tcgen05: the partial tile of %d tokens does not fit the stage ring", M);
@@ -411,20 +464,58 @@ static int gemm(const void* x, const void* w, void* out, int out_dtype, int* sta
         if (out_dtype != RV_DTYPE_BF16 || M > 16)
             RV_FAIL("gemm_tcgen05: the q|k|v epilogue takes bfloat16 and up to 16 tokens");
         return launch<bf16, true>(map_w, map_x, out, status, M, N, kblocks, n_pad, stages, tiles, splits,
-                                  smem, *epi, s);
+                                  smem, *epi, w_tiled, kbs, s);
     }
     if (out_dtype == RV_DTYPE_BF16)
         return launch<bf16, false>(map_w, map_x, out, status, M, N, kblocks, n_pad, stages, tiles, splits,
-                                   smem, none, s);
+                                   smem, none, w_tiled, kbs, s);
     if (out_dtype == RV_DTYPE_F32)
         return launch<float, false>(map_w, map_x, out, status, M, N, kblocks, n_pad, stages, tiles,
-                                    splits, smem, none, s);
+                                    splits, smem, none, w_tiled, kbs, s);
     RV_FAIL("gemm_tcgen05: unknown output dtype code %d", out_dtype);
 }
 
+// `w_tiled` (may be null): the same matrix as written by rv_gemm_tile_weights.
 extern "C" int rv_gemm_tcgen05(const void* x, const void* w, void* out, int out_dtype, int* status,
-                               int M, int N, int K, void* stream) {
-    return gemm(x, w, out, out_dtype, status, M, N, K, nullptr, stream);
+                               int M, int N, int K, const void* w_tiled, void* stream) {
+    return gemm(x, w, out, out_dtype, status, M, N, K, nullptr, w_tiled, stream);
+}
+
+// The weight matrix laid out for contiguous copies: tile (t, kb) = rows [128 t, 128 t + 128) x
+// columns [64 kb, 64 kb + 64) of W [N, K] as the 16 KB image the MMA reads from shared memory
+// (rows of 128 bytes whose 16-byte chunks are XOR-swizzled with the row index mod 8), tiles in
+// (t, kb) order, rows and columns past the matrix as zeros.
+__global__ void tile_weights_kernel(const bf16* __restrict__ w, uint4* __restrict__ out, int N, int K,
+                                    int kblocks, long long chunks) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < chunks;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int ch = (int)(i & 7), r = (int)((i >> 3) & 127);
+        const long long tile_kb = i >> 10;                       // 1024 chunks of 16 bytes per tile
+        const int kb = (int)(tile_kb % kblocks);
+        const long long t = tile_kb / kblocks;
+        const long long row = t * RV_GEMM_BM + r;
+        const int col = kb * RV_GEMM_BK + ((ch ^ (r & 7)) << 3);
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (row < N && col < K) v = *(const uint4*)(w + row * K + col);        // K is a multiple of 8
+        out[i] = v;
+    }
+}
+
+extern "C" long long rv_gemm_tiled_bytes(int N, int K) {
+    const long long tiles = (N + RV_GEMM_BM - 1) / RV_GEMM_BM, kblocks = (K + RV_GEMM_BK - 1) / RV_GEMM_BK;
+    return tiles * kblocks * RV_GEMM_BM * RV_GEMM_BK * 2;
+}
+
+extern "C" int rv_gemm_tile_weights(const void* w, void* out, int N, int K, void* stream) {
+    if (N <= 0 || K <= 0 || K % 8 || ((uintptr_t)w | (uintptr_t)out) % 16)
+        RV_FAIL("gemm_tile_weights: K = %d must be a multiple of 8 and the buffers 16-byte aligned", K);
+    const int kblocks = (K + RV_GEMM_BK - 1) / RV_GEMM_BK;
+    const long long chunks = rv_gemm_tiled_bytes(N, K) / 16;
+    const int blocks = (int)((chunks + 255) / 256 < 148 * 32 ? (chunks + 255) / 256 : 148 * 32);
+    tile_weights_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>((const bf16*)w, (uint4*)out, N, K,
+                                                                   kblocks, chunks);
+    RV_CHECK_LAUNCH("gemm_tile_weights");
+    return 0;
 }
 
 // out[M, N] gets the normalised, rotated queries (its key and value columns are not written);
@@ -436,7 +527,7 @@ extern "C" int rv_gemm_tcgen05_qkv(const void* x, const void* w, void* out, int*
                                    const float* q_weight, const float* k_weight, float eps,
                                    const float* cos_table, const float* sin_table,
                                    const int* positions, const int* slot_mapping, void* k_cache,
-                                   void* v_cache, void* stream) {
+                                   void* v_cache, const void* w_tiled, void* stream) {
     if (N != (num_heads + 2 * num_kv_heads) * 64)
         RV_FAIL("gemm_tcgen05_qkv: N = %d is not (heads + 2 kv heads) * 64", N);
     if (!slot_mapping || !k_cache || !v_cache || (cos_table && (!sin_table || !positions)))
@@ -453,5 +544,5 @@ extern "C" int rv_gemm_tcgen05_qkv(const void* x, const void* w, void* out, int*
     epi.eps = eps;
     epi.num_heads = num_heads;
     epi.num_kv_heads = num_kv_heads;
-    return gemm(x, w, out, RV_DTYPE_BF16, status, M, N, K, &epi, stream);
+    return gemm(x, w, out, RV_DTYPE_BF16, status, M, N, K, &epi, w_tiled, stream);
 }

@@ -53,6 +53,14 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map,
         ::"r"(smem_u32(dst)), "l"((unsigned long long)map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
         : "memory");
 }
+// 1-D bulk copy of `bytes` contiguous bytes (a multiple of 16, both addresses 16-byte aligned).
+__device__ __forceinline__ void bulk_load_1d(void* dst, const void* src, unsigned bytes,
+                                             unsigned long long* bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar))
+        : "memory");
+}
 __device__ __forceinline__ void tcgen05_commit(unsigned long long* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
                  ::"r"(smem_u32(bar))

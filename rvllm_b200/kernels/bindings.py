@@ -49,6 +49,7 @@ class CudaOps:
         self.launches = 0
         self.lib.rv_last_error.restype = ctypes.c_char_p
         self.lib.rv_paged_attention_decode_scratch_bytes.restype = c_longlong
+        self.lib.rv_gemm_tiled_bytes.restype = c_longlong
         self._scratch = {}
         self._retired = []
         self._attn_libs = {}
@@ -75,6 +76,8 @@ class CudaOps:
         self.gemm_small_m = int(os.environ.get("RVLLM_GEMM_SMALL_M", "16"))
         self.gemm_mode = os.environ.get("RVLLM_GEMM", "tcgen05")
         self._gemm_state = {}
+        self._tiled = {}
+        self.gemm_tiled = os.environ.get("RVLLM_GEMM_TILED", "1") != "0"
         # q/k norm + rotation + cache write inside the q|k|v product's epilogue (few bfloat16
         # tokens, head size 64); "0": always the separate kernel
         self.fuse_qkv_rope = os.environ.get("RVLLM_FUSE_QKV_ROPE", "1") == "1"
@@ -162,8 +165,34 @@ class CudaOps:
         y = torch.empty((m, n), dtype=out_dtype, device=x.device)
         self._check(self.lib.rv_gemm_tcgen05(
             _ptr(x), _ptr(w), _ptr(y), _code(out_dtype), _ptr(self._gemm_status(x.device)),
-            c_int(m), c_int(n), c_int(k), self._stream()), "gemm_tcgen05")
+            c_int(m), c_int(n), c_int(k), _ptr(self._tiled_weight(w)), self._stream()),
+            "gemm_tcgen05")
         return y
+
+    def _tiled_weight(self, w):
+        """The weight matrix once more, laid out tile by tile for the streaming product
+        (`rv_gemm_tile_weights`): made the first time a matrix is used with few tokens and
+        kept as long as the matrix lives.  It doubles the memory of the matrices that decode
+        steps multiply (2.3 GB at LFM2-1.2B sizes) and lets an SM copy a tile as one
+        contiguous 16 KB instead of 128 strided rows.  RVLLM_GEMM_TILED=0: not made."""
+        if not self.gemm_tiled:
+            return None
+        key = (w.data_ptr(), tuple(w.shape))
+        hit = self._tiled.get(key)
+        if hit is not None and hit[0]() is w:
+            return hit[1]
+        if torch.cuda.is_current_stream_capturing():
+            return None                    # no allocation inside a capture: the box copies do
+        n, k = w.shape
+        nbytes = int(self.lib.rv_gemm_tiled_bytes(c_int(n), c_int(k)))
+        tiled = torch.empty(nbytes, dtype=torch.uint8, device=w.device)
+        self._check(self.lib.rv_gemm_tile_weights(_ptr(w), _ptr(tiled), c_int(n), c_int(k),
+                                                  self._stream()), "gemm_tile_weights")
+        import weakref
+        self._tiled[key] = (weakref.ref(w), tiled)
+        if len(self._tiled) > 4096:        # matrices that died: drop their copies
+            self._tiled = {kk: v for kk, v in self._tiled.items() if v[0]() is not None}
+        return tiled
 
     def status_word(self, device) -> torch.Tensor:
         """The int32 word in which kernels on `device` record a wait that ran out (0: none).
@@ -219,8 +248,8 @@ class CudaOps:
                 _ptr(x), _ptr(w_qkv), _ptr(qkv), _ptr(self._gemm_status(x.device)), c_int(m),
                 c_int(n), c_int(k), c_int(num_heads), c_int(num_kv_heads), _ptr(q_weight),
                 _ptr(k_weight), c_float(eps), _ptr(cos), _ptr(sin), _ptr(positions),
-                _ptr(slot_mapping), _ptr(k_cache), _ptr(v_cache), self._stream()),
-                "gemm_tcgen05_qkv")
+                _ptr(slot_mapping), _ptr(k_cache), _ptr(v_cache), _ptr(self._tiled_weight(w_qkv)),
+                self._stream()), "gemm_tcgen05_qkv")
             return qkv
         qkv = self.linear(x, w_qkv, out_dtype=out_dtype)
         self.qk_norm_rope_write(qkv, num_heads, num_kv_heads, head_dim, q_weight, k_weight, eps,

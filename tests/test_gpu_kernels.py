@@ -519,6 +519,33 @@ def test_gemm_tcgen05(ops, M, N, K, out_dtype):
 
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 128, 64), (3, 200, 72), (8, 2048, 2048), (16, 6144, 2048),
+                                   (5, 2048, 8192), (16, 1000, 520), (64, 2048, 8192)])
+def test_gemm_tiled_weights(ops, M, N, K):
+    """With the weight matrix laid out tile by tile (contiguous bulk copies of two K blocks a
+    stage) and with tensor-map boxes of the row-major matrix the MMAs run over the same values in
+    the same order: bit-identical results, for tiles and K blocks that the matrix fills only
+    partly, K split over a cluster and not; the tiled copy is made once per matrix."""
+    g = torch.Generator().manual_seed(13)
+    x = rnd((M, K), torch.bfloat16, g).cuda()
+    w = rnd((N, K), torch.bfloat16, g, 0.05).cuda()
+    was = ops.gemm_tiled
+    try:
+        ops.gemm_tiled = True
+        a = ops.linear_tcgen05(x, w, torch.float32)
+        copies = len(ops._tiled)
+        a2 = ops.linear_tcgen05(x, w, torch.float32)
+        assert len(ops._tiled) == copies                      # the same copy again
+        ops.gemm_tiled = False
+        b = ops.linear_tcgen05(x, w, torch.float32)
+    finally:
+        ops.gemm_tiled = was
+    ops.check_status()
+    assert torch.equal(a, b) and torch.equal(a, a2)
+    ref = x.double() @ w.double().t()
+    assert float((a.double() - ref).abs().max() / ref.abs().max()) <= 2e-5
+
+
 PREFILL_CASES = [
     # q_lens, ctx_lens, heads, kv heads, head size, page size, window.  Head size 64: the
     # tcgen05 kernel (128 rows = tokens x heads of a group, tiles of 64 keys): group sizes
