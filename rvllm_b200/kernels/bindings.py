@@ -189,9 +189,9 @@ class CudaOps:
         self._check(self.lib.rv_gemm_tile_weights(_ptr(w), _ptr(tiled), c_int(n), c_int(k),
                                                   self._stream()), "gemm_tile_weights")
         import weakref
+        # the copies of matrices that have died go first (a model that was unloaded)
+        self._tiled = {kk: v for kk, v in self._tiled.items() if v[0]() is not None}
         self._tiled[key] = (weakref.ref(w), tiled)
-        if len(self._tiled) > 4096:        # matrices that died: drop their copies
-            self._tiled = {kk: v for kk, v in self._tiled.items() if v[0]() is not None}
         return tiled
 
     def status_word(self, device) -> torch.Tensor:

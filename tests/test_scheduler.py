@@ -180,3 +180,18 @@ def test_seeded_sampling_counts_per_request():
             Request("b", [9], 3, sampling=SamplingParams(0.8, 1.0, 6), arrival_step=1)]
     run(runner, reqs, SchedulerConfig(block_size=4, num_blocks=64), 256, sampler=Recorder())
     assert seen[0] == [0] and [1, 0] in seen and [2, 1] in seen
+
+
+def test_settled_heap_freezes_and_gives_back(monkeypatch):
+    """Inside, what was on the heap is in the permanent generation (the collector's passes skip
+    it); afterwards nothing is left there; RVLLM_GC_FREEZE=0 leaves the collector alone."""
+    import gc
+
+    from rvllm_b200.engine import settled_heap
+    gc.unfreeze()
+    with settled_heap():
+        assert gc.get_freeze_count() > 0
+    assert gc.get_freeze_count() == 0
+    monkeypatch.setenv("RVLLM_GC_FREEZE", "0")
+    with settled_heap():
+        assert gc.get_freeze_count() == 0
