@@ -490,23 +490,83 @@ def run_kernels(args):
                 "us": round(us, 1), "GB/s": round(nbytes / us / 1e3, 1),
                 "frac_hbm": round(nbytes / us / 1e3 / pk["hbm_gbs"], 3)}
     if args.kernel in ("all", "attn_prefill"):
+        # the whole prompt in one portion, and (--kernel-ctx above the portion) its last portion:
+        # the same number of query tokens at the end of a longer context
         T = PREFILL_TOKENS
+        for C in sorted({T, max(T, args.kernel_ctx if args.kernel == "attn_prefill" else T)}):
+            blocks = -(-C // ps)
+            kc = torch.randn(blocks, ps, nkv, hd, device="cuda", dtype=torch.bfloat16)
+            vc = torch.randn_like(kc)
+            table = torch.randperm(blocks, device="cuda").to(torch.int32).view(1, blocks)
+            q = torch.randn(T, (nh + 2 * nkv) * hd, device="cuda", dtype=torch.bfloat16)
+            o = torch.empty(T, nh * hd, device="cuda", dtype=torch.bfloat16)
+            ctx = SimpleNamespace(n_tokens=T, n_reqs=1, n_decode=0, max_ctx_len=C, max_q_len=T,
+                                  q_start=torch.tensor([0, T], dtype=torch.int32, device="cuda"),
+                                  ctx_lens=torch.tensor([C], dtype=torch.int32, device="cuda"),
+                                  token_req=torch.zeros(T, dtype=torch.int32, device="cuda"))
+            group = SimpleNamespace(block_table=table, max_blocks=blocks, page_size=ps, window=None)
+            us = graph_time([lambda: ops.paged_attention(q, nh, nkv, hd, kc, vc, ctx, group,
+                                                         1 / math.sqrt(hd), None, o)] * 4)
+            flops = 4 * nh * hd * (T * (C - T) + T * (T + 1) / 2)
+            name = f"attn_prefill_t{T}" + (f"_ctx{C}" if C != T else "")
+            out[name] = {"us": round(us, 1), "TFLOP/s": round(flops / us / 1e6, 1),
+                         "frac_bf16": round(flops / us / 1e6 / pk["bf16_tflops"], 3)}
+    if args.kernel == "elementwise":
+        # the memory-bound kernels between the products of a 2,048-token prompt portion, each on
+        # buffers in rotation that together exceed the L2 (bytes = what the kernel has to move)
+        T = PREFILL_TOKENS
+        cfgd = dict(LFM2_1_2B)
+        cfgd.update(SIZES[args.size])
+        from rvllm_b200.config import config_from_dict
+        mc = config_from_dict(cfgd)
+        H, F, taps = mc.hidden_size, mc.ffn_dim, mc.conv_L_cache
+        bf = torch.bfloat16
+        n = 6
+        res = {}
+
+        def timed(name, fns, nbytes):
+            us = graph_time(fns)
+            res[name] = {"us": round(us, 1), "GB/s": round(nbytes / us / 1e3, 1),
+                         "frac_hbm": round(nbytes / us / 1e3 / pk["hbm_gbs"], 3)}
+
+        gu = [torch.randn(T, 2 * F, device="cuda", dtype=bf) for _ in range(n)]
+        act = [torch.empty(T, F, device="cuda", dtype=bf) for _ in range(n)]
+        timed("swiglu", [(lambda a=a, b=b: ops.swiglu(a, b)) for a, b in zip(gu, act)], T * F * 6)
+        del gu, act
+        resid = [torch.randn(T, H, device="cuda", dtype=torch.float32) for _ in range(n * 2)]
+        delta = [torch.randn(T, H, device="cuda", dtype=bf) for _ in range(n * 2)]
+        outs = [torch.empty(T, H, device="cuda", dtype=bf) for _ in range(n * 2)]
+        wn = torch.ones(H, device="cuda", dtype=torch.float32)
+        timed("add_rmsnorm", [(lambda r=r, d=d, o=o: ops.add_rmsnorm(r, d, wn, 1e-5, o))
+                              for r, d, o in zip(resid, delta, outs)], T * H * 12)
+        del resid, delta
+        proj = [torch.randn(T, 3 * H, device="cuda", dtype=bf) for _ in range(n * 2)]
+        filt = torch.randn(H, taps, device="cuda", dtype=torch.float32)
+        state = torch.zeros(2, taps - 1, H, device="cuda", dtype=torch.float32)
+        cctx = SimpleNamespace(n_reqs=1, max_q_len=T,
+                               q_start=torch.tensor([0, T], dtype=torch.int32, device="cuda"),
+                               state_slot=torch.tensor([1], dtype=torch.int32, device="cuda"),
+                               start_pos=torch.tensor([0], dtype=torch.int32, device="cuda"))
+        timed("short_conv", [(lambda a=a, o=o: ops.short_conv(a, filt, None, None, state, cctx, o))
+                             for a, o in zip(proj, outs)], T * H * 8)
+        del proj
+        qkv = [torch.randn(T, (nh + 2 * nkv) * hd, device="cuda", dtype=bf) for _ in range(n * 3)]
         blocks = -(-T // ps)
-        kc = torch.randn(blocks, ps, nkv, hd, device="cuda", dtype=torch.bfloat16)
-        vc = torch.randn_like(kc)
-        table = torch.randperm(blocks, device="cuda").to(torch.int32).view(1, blocks)
-        q = torch.randn(T, (nh + 2 * nkv) * hd, device="cuda", dtype=torch.bfloat16)
-        o = torch.empty(T, nh * hd, device="cuda", dtype=torch.bfloat16)
-        ctx = SimpleNamespace(n_tokens=T, n_reqs=1, n_decode=0, max_ctx_len=T, max_q_len=T,
-                              q_start=torch.tensor([0, T], dtype=torch.int32, device="cuda"),
-                              ctx_lens=torch.tensor([T], dtype=torch.int32, device="cuda"),
-                              token_req=torch.zeros(T, dtype=torch.int32, device="cuda"))
-        group = SimpleNamespace(block_table=table, max_blocks=blocks, page_size=ps, window=None)
-        us = graph_time([lambda: ops.paged_attention(q, nh, nkv, hd, kc, vc, ctx, group,
-                                                     1 / math.sqrt(hd), None, o)] * 4)
-        flops = 4 * nh * hd * T * (T + 1) / 2
-        out[f"attn_prefill_t{T}"] = {"us": round(us, 1), "TFLOP/s": round(flops / us / 1e6, 1),
-                                     "frac_bf16": round(flops / us / 1e6 / pk["bf16_tflops"], 3)}
+        kcs = [torch.empty(blocks, ps, nkv, hd, device="cuda", dtype=bf) for _ in range(n * 3)]
+        vcs = [torch.empty_like(k) for k in kcs]
+        pos = torch.arange(T, dtype=torch.int32, device="cuda")
+        slots = torch.randperm(blocks * ps, device="cuda").to(torch.int32)[:T].contiguous()
+        qw = torch.ones(hd, device="cuda", dtype=torch.float32)
+        inv = 1.0 / (1e6 ** (torch.arange(0, hd, 2, device="cuda", dtype=torch.float32) / hd))
+        ang = pos.float()[:, None] * inv[None, :]
+        table = (ang.cos().contiguous(), ang.sin().contiguous())
+        timed("qk_norm_rope_write",
+              [(lambda a=a, k=k, v=v: ops.qk_norm_rope_write(a, nh, nkv, hd, qw, qw, 1e-5, table, pos,
+                                                            slots, k, v))
+               for a, k, v in zip(qkv, kcs, vcs)],
+              T * hd * 2 * ((nh + nkv) * 2 + nkv + 2 * nkv))
+        print(json.dumps({"only": "kernels", "peaks": pk["source"], "tokens": T, **res}))
+        return 0
     if args.kernel == "all" or args.kernel.startswith("gemm"):
         M = args.kernel_m
         x = torch.randn(M, 8192, device="cuda", dtype=torch.bfloat16)
@@ -760,7 +820,7 @@ def main():
     ap.add_argument("--workload", default="350m-mixed", choices=sorted(WORKLOADS),
                     help="with --only workload: which one")
     ap.add_argument("--kernel", default="all",
-                    help="with --only kernels: attn_decode, attn_prefill, gemm, gemm:NxK, copy_rate or all")
+                    help="with --only kernels: attn_decode, attn_prefill, gemm, gemm:NxK, elementwise, copy_rate or all")
     ap.add_argument("--kernel-batch", type=int, default=64)
     ap.add_argument("--kernel-m", type=int, default=8, help="tokens of the gemm micro-benchmark")
     ap.add_argument("--kernel-ctx", type=int, default=4096)

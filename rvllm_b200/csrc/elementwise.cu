@@ -211,25 +211,38 @@ __global__ void swiglu_kernel(const T* __restrict__ in, T* __restrict__ out, int
     }
 }
 
-// bfloat16, 8 elements per thread (16-byte loads); needs ffn % 8 == 0.
+// bfloat16, 8 elements per access (16-byte loads); needs ffn % 8 == 0.  A thread requests the
+// gate and up values of two positions before it uses either; index arithmetic is 32-bit when the
+// element count allows.
+__device__ __forceinline__ uint4 rv_swiglu8(const uint4 g4, const uint4 u4) {
+    uint4 o4;
+    const __nv_bfloat162* g2 = (const __nv_bfloat162*)&g4;
+    const __nv_bfloat162* u2 = (const __nv_bfloat162*)&u4;
+    __nv_bfloat162* o2 = (__nv_bfloat162*)&o4;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const float2 g = __bfloat1622float2(g2[k]), u = __bfloat1622float2(u2[k]);
+        // the quotient is rounded to bfloat16 below: the fast division's last float32 bits do not
+        // show (the float32 kernel above divides exactly)
+        o2[k] = __floats2bfloat162_rn(__fdividef(g.x, 1.f + __expf(-g.x)) * u.x,
+                                      __fdividef(g.y, 1.f + __expf(-g.y)) * u.y);
+    }
+    return o4;
+}
+
+template <typename IDX>
 __global__ void swiglu_bf16x8_kernel(const uint4* __restrict__ in, uint4* __restrict__ out,
                                      int ffn8, size_t total8) {
     rv_pdl_prologue();
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total8;
-         i += (size_t)gridDim.x * blockDim.x) {
-        const size_t n = i / ffn8;
-        const int f = (int)(i - n * ffn8);
-        uint4 g4 = in[n * 2 * ffn8 + f], u4 = in[n * 2 * ffn8 + ffn8 + f], o4;
-        const __nv_bfloat162* g2 = (const __nv_bfloat162*)&g4;
-        const __nv_bfloat162* u2 = (const __nv_bfloat162*)&u4;
-        __nv_bfloat162* o2 = (__nv_bfloat162*)&o4;
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            const float2 g = __bfloat1622float2(g2[k]), u = __bfloat1622float2(u2[k]);
-            o2[k] = __floats2bfloat162_rn(g.x / (1.f + __expf(-g.x)) * u.x,
-                                          g.y / (1.f + __expf(-g.y)) * u.y);
-        }
-        out[i] = o4;
+    const IDX step = (IDX)gridDim.x * blockDim.x, n8 = (IDX)total8, f8 = (IDX)ffn8;
+    for (IDX i = (IDX)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += 2 * step) {
+        const IDX j = i + step;
+        const bool two = j < n8;
+        const IDX ni = i / f8, nj = two ? j / f8 : ni;
+        const IDX pi = ni * f8 + i, pj = two ? nj * f8 + j : pi;      // = n * 2 * ffn8 + f
+        const uint4 gi = in[pi], ui = in[pi + f8], gj = in[pj], uj = in[pj + f8];
+        out[i] = rv_swiglu8(gi, ui);
+        if (two) out[j] = rv_swiglu8(gj, uj);
     }
 }
 
@@ -242,7 +255,12 @@ extern "C" int rv_swiglu(const void* in, void* out, int dtype, int n_rows, int f
         ((uintptr_t)out % 16 == 0)) {
         const size_t total8 = total / 8;
         const int blocks = (int)((total8 + 255) / 256 < 148 * 16 ? (total8 + 255) / 256 : 148 * 16);
-        rv_launch(swiglu_bf16x8_kernel, dim3(blocks), dim3(256), 0, s, (const uint4*)in, (uint4*)out, ffn / 8, total8);
+        if (total8 * 2 < 0x7fffffffull)
+            rv_launch(swiglu_bf16x8_kernel<unsigned>, dim3(blocks), dim3(256), 0, s, (const uint4*)in,
+                      (uint4*)out, ffn / 8, total8);
+        else
+            rv_launch(swiglu_bf16x8_kernel<size_t>, dim3(blocks), dim3(256), 0, s, (const uint4*)in,
+                      (uint4*)out, ffn / 8, total8);
     } else {
         const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
         RV_DISPATCH_DTYPE(dtype, "swiglu",

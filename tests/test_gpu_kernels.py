@@ -409,6 +409,46 @@ def test_short_conv(ops, dtype, taps, bias):
         assert torch.allclose(d_state.cpu(), ref_state, atol=1e-6, rtol=1e-6)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("taps", [3, 4])
+def test_short_conv_long_portion_equals_short_portions(ops, dtype, taps):
+    """A portion of 150 tokens (the kernel for long portions: eight channels a thread, rows
+    requested ahead) gives bit for bit what portions of 40 + 63 + 47 tokens give through the
+    state (the kernel for short ones), and the same final state."""
+    g = torch.Generator().manual_seed(91)
+    hidden, n = 328, 150
+    proj = rnd((n, 3 * hidden), dtype, g).cuda()
+    filt = rnd((hidden, taps), torch.float32, g, 0.5).cuda()
+    b_in = rnd((3 * hidden,), torch.float32, g, 0.1).cuda()
+    b_conv = rnd((hidden,), torch.float32, g, 0.1).cuda()
+
+    def run(cuts):
+        state = torch.zeros(2, taps - 1, hidden, dtype=torch.float32, device="cuda")
+        out = torch.empty(n, hidden, dtype=dtype, device="cuda")
+        pos = 0
+        for ql in cuts:
+            ctx = SimpleNamespace(n_reqs=1, max_q_len=ql,
+                                  q_start=torch.tensor([0, ql], dtype=torch.int32, device="cuda"),
+                                  state_slot=torch.tensor([1], dtype=torch.int32, device="cuda"),
+                                  start_pos=torch.tensor([pos], dtype=torch.int32, device="cuda"))
+            ops.short_conv(proj[pos:pos + ql], filt, b_in, b_conv, state, ctx, out[pos:pos + ql])
+            pos += ql
+        return out, state
+
+    whole, whole_state = run([n])
+    parts, parts_state = run([40, 63, 47])
+    assert torch.equal(whole, parts)
+    assert torch.equal(whole_state, parts_state)
+    ref = torch.empty(n, hidden, dtype=dtype)
+    ref_state = torch.zeros(2, taps - 1, hidden)
+    ctx = SimpleNamespace(n_reqs=1, max_q_len=n, q_start=torch.tensor([0, n], dtype=torch.int32),
+                          state_slot=torch.tensor([1], dtype=torch.int32),
+                          start_pos=torch.tensor([0], dtype=torch.int32))
+    PlainOps().short_conv(proj.cpu(), filt.cpu(), b_in.cpu(), b_conv.cpu(), ref_state, ctx, ref)
+    assert torch.allclose(whole.cpu().float(), ref.float(), **tol(dtype))
+    assert torch.allclose(whole_state.cpu(), ref_state, atol=1e-6, rtol=1e-6)
+
+
 def test_argmax_first_maximum_and_nan(ops):
     x = torch.randn(5, 1003)
     x[0, 17] = x[0, 900] = 9.0                 # tie: the first wins
