@@ -167,13 +167,15 @@ __global__ void __launch_bounds__(192, 3) paged_attention_prefill_tcgen05_kernel
     int window, int* __restrict__ status) {
     static_assert(HD == 64, "one 128-byte swizzle row per key");
     rv_pdl_prologue();
-    const int r = first_req + blockIdx.z, g = blockIdx.y;
+    // blocks are handed out in the order x, then y: with the key/value head in x, all heads of a
+    // request's longest block of query tokens start first, then all heads of the next longest
+    const int r = first_req + blockIdx.z, g = blockIdx.x;
     const int clen = ctx_lens[r];
     const int qs = q_start[r];
     const int qlen = q_start[r + 1] - qs;
     const int nqb = (qlen + q_block - 1) / q_block;
-    if ((int)blockIdx.x >= nqb || clen == 0) return;           // the whole block, before any set-up
-    const int qb = nqb - 1 - blockIdx.x;                        // the longest blocks start first
+    if ((int)blockIdx.y >= nqb || clen == 0) return;           // the whole block, before any set-up
+    const int qb = nqb - 1 - blockIdx.y;                        // the longest blocks start first
     const int G = num_heads / num_kv_heads;
     const int q0 = qb * q_block;
     const int n_tok = min(q_block, qlen - q0);                  // query tokens of this block
@@ -568,7 +570,7 @@ extern "C" int AT_SYM(rv_paged_attention_prefill_tcgen05)(
         configured = true;
     }
     const int nqb = (max_q_len + q_block - 1) / q_block;
-    rv_launch(paged_attention_prefill_tcgen05_kernel<RV_HD>, dim3(nqb, num_kv_heads, n_reqs),
+    rv_launch(paged_attention_prefill_tcgen05_kernel<RV_HD>, dim3(num_kv_heads, nqb, n_reqs),
               dim3(192), smem, (cudaStream_t)stream, map_q, map_k, map_v, block_table, max_blocks,
               q_start, ctx_lens, (bf16*)out, first_req, num_heads, num_kv_heads, q_block, page_size,
               scale * 1.4426950408889634f, window, status);
