@@ -409,7 +409,7 @@ def run_kernels(args):
     from rvllm_b200.kernels import cuda_ops
     ops = cuda_ops()
     pk = peaks()
-    nh, nkv, hd, ps = 32, 8, 64, PAGE
+    nh, nkv, hd, ps = 32, 8, 64, args.kernel_page
     out = {"only": "kernels", "peaks": pk["source"]}
 
     def graph_time(fns, reps=5):
@@ -824,6 +824,7 @@ def main():
     ap.add_argument("--kernel-batch", type=int, default=64)
     ap.add_argument("--kernel-m", type=int, default=8, help="tokens of the gemm micro-benchmark")
     ap.add_argument("--kernel-ctx", type=int, default=4096)
+    ap.add_argument("--kernel-page", type=int, default=PAGE, help="page size of the attention micro-benchmarks")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
