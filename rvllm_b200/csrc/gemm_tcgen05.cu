@@ -73,11 +73,16 @@ struct RvQkvEpilogue {
 // query and key head is RMS-normalised and rotated, queries go to `out`, keys and values to
 // their slots of the paged cache: the separate kernel for that, and its place in the chain of
 // dependent launches, are gone.
+// A plain product carries no epilogue arguments at all.
+struct RvNoEpilogue {};
+template <bool QKV> struct RvEpilogueOf { typedef RvNoEpilogue type; };
+template <> struct RvEpilogueOf<true> { typedef RvQkvEpilogue type; };
+
 template <typename TO, bool QKV, int KBS>
 __global__ void __launch_bounds__(128) gemm_tcgen05_kernel(
     const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
     TO* __restrict__ out, int* __restrict__ status, int M, int N, int kblocks, int n_pad,
-    int stages, const RvQkvEpilogue epi, const bf16* __restrict__ w_tiled) {
+    int stages, const typename RvEpilogueOf<QKV>::type epi, const bf16* __restrict__ w_tiled) {
     constexpr int kbs = KBS;          // K blocks of 64 per stage
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // the dynamic segment is aligned by hand: swizzled tiles need 1024-byte alignment
@@ -252,7 +257,7 @@ __global__ void __launch_bounds__(128) gemm_tcgen05_kernel(
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
                      "r"(tmem_cols));
     }
-    if (QKV) {
+    if constexpr (QKV) {
         // ---- q|k|v: this block finishes its tokens (t = split, split + splits, ...) ------------
         __shared__ float red[4];
         __shared__ float xs[RV_GEMM_BM];
@@ -394,6 +399,10 @@ extern "C" int rv_gemm_tcgen05_init() {
     return 0;
 }
 
+template <bool QKV> static typename RvEpilogueOf<QKV>::type pass_epi(const RvQkvEpilogue& e);
+template <> RvNoEpilogue pass_epi<false>(const RvQkvEpilogue&) { return RvNoEpilogue{}; }
+template <> RvQkvEpilogue pass_epi<true>(const RvQkvEpilogue& e) { return e; }
+
 template <typename TO, bool QKV, int KBS>
 static int launch_kbs(const CUtensorMap& map_w, const CUtensorMap& map_x, void* out, int* status, int M,
                   int N, int kblocks, int n_pad, int stages, int tiles, int splits, size_t smem,
@@ -413,7 +422,7 @@ static int launch_kbs(const CUtensorMap& map_w, const CUtensorMap& map_x, void* 
     cfg.attrs = attr;
     cfg.numAttrs = 2;
     cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<TO, QKV, KBS>, map_w, map_x, (TO*)out,
-                                       status, M, N, kblocks, n_pad, stages, epi, (const bf16*)w_tiled);
+                                       status, M, N, kblocks, n_pad, stages, pass_epi<QKV>(epi), (const bf16*)w_tiled);
     if (e != cudaSuccess) RV_FAIL("gemm_tcgen05: %s", cudaGetErrorString(e));
     return 0;
 }
