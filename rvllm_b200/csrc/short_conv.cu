@@ -220,7 +220,13 @@ __global__ void short_conv_vec4_kernel(const T* __restrict__ proj, const float* 
         for (int k = 0; k < RV_CONV_VEC_TAPS - 1; ++k)
             if (k == hist - 1) win[k] = bx;
     }
-    if (t0 == 0 && st && hist > 0) {
+    if (t0 == 0 && st && hist > 0 && qlen <= RV_CONV_CHUNK) {
+        // the whole portion went through this thread: the window it ends with is the new state
+        // (nothing is read again, so a single token's step has one dependent load fewer)
+#pragma unroll
+        for (int i = 0; i < RV_CONV_VEC_TAPS - 1; ++i)
+            if (i < hist) *(float4*)(st + (size_t)i * hidden) = win[i];
+    } else if (t0 == 0 && st && hist > 0) {
 #pragma unroll
         for (int i = 0; i < RV_CONV_VEC_TAPS - 1; ++i) {
             if (i < hist) {
