@@ -218,9 +218,9 @@ def settled_heap():
     a workload's time.  On entry garbage is collected once and what remains is moved to the
     permanent generation (`gc.freeze`), which later passes skip; on exit it is moved back.
     Objects made inside are collected as usual.  RVLLM_GC_FREEZE=0 turns it off."""
-    if os.environ.get("RVLLM_GC_FREEZE", "1") == "0":
-        yield
-        return
+    if os.environ.get("RVLLM_GC_FREEZE", "1") == "0" or gc.get_freeze_count() > 0:
+        yield                      # switched off, or the caller has frozen the heap already:
+        return                     # `gc.unfreeze` below would thaw their objects too
     gc.collect()
     gc.freeze()
     try:

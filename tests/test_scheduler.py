@@ -192,6 +192,12 @@ def test_settled_heap_freezes_and_gives_back(monkeypatch):
     with settled_heap():
         assert gc.get_freeze_count() > 0
     assert gc.get_freeze_count() == 0
+    gc.freeze()                               # a caller's own freeze is left as it is
+    mine = gc.get_freeze_count()
+    with settled_heap():
+        pass
+    assert gc.get_freeze_count() >= mine > 0
+    gc.unfreeze()
     monkeypatch.setenv("RVLLM_GC_FREEZE", "0")
     with settled_heap():
         assert gc.get_freeze_count() == 0
