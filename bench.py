@@ -492,7 +492,7 @@ def run_kernels(args):
     if args.kernel in ("all", "attn_prefill"):
         # the whole prompt in one portion, and (--kernel-ctx above the portion) its last portion:
         # the same number of query tokens at the end of a longer context
-        T = PREFILL_TOKENS
+        T = args.kernel_tokens
         for C in sorted({T, max(T, args.kernel_ctx if args.kernel == "attn_prefill" else T)}):
             blocks = -(-C // ps)
             kc = torch.randn(blocks, ps, nkv, hd, device="cuda", dtype=torch.bfloat16)
@@ -824,6 +824,8 @@ def main():
     ap.add_argument("--kernel-batch", type=int, default=64)
     ap.add_argument("--kernel-m", type=int, default=8, help="tokens of the gemm micro-benchmark")
     ap.add_argument("--kernel-ctx", type=int, default=4096)
+    ap.add_argument("--kernel-tokens", type=int, default=PREFILL_TOKENS,
+                    help="query tokens of the prefill attention micro-benchmark")
     ap.add_argument("--kernel-page", type=int, default=PAGE, help="page size of the attention micro-benchmarks")
     args = ap.parse_args()
     if args.impl == "reference":
