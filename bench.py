@@ -409,7 +409,7 @@ def run_kernels(args):
     from rvllm_b200.kernels import cuda_ops
     ops = cuda_ops()
     pk = peaks()
-    nh, nkv, hd, ps = 32, 8, 64, args.kernel_page
+    nh, nkv, hd, ps = args.kernel_heads, 8, 64, args.kernel_page
     out = {"only": "kernels", "peaks": pk["source"]}
 
     def graph_time(fns, reps=5):
@@ -826,6 +826,8 @@ def main():
     ap.add_argument("--kernel-ctx", type=int, default=4096)
     ap.add_argument("--kernel-tokens", type=int, default=PREFILL_TOKENS,
                     help="query tokens of the prefill attention micro-benchmark")
+    ap.add_argument("--kernel-heads", type=int, default=32,
+                    help="query heads of the attention micro-benchmarks (8 key/value heads)")
     ap.add_argument("--kernel-page", type=int, default=PAGE, help="page size of the attention micro-benchmarks")
     args = ap.parse_args()
     if args.impl == "reference":

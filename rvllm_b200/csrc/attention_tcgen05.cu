@@ -164,12 +164,17 @@ __global__ void __launch_bounds__(192, 3) paged_attention_prefill_tcgen05_kernel
     const __grid_constant__ CUtensorMap map_v, const int* __restrict__ block_table, int max_blocks,
     const int* __restrict__ q_start, const int* __restrict__ ctx_lens, bf16* __restrict__ out,
     int first_req, int num_heads, int num_kv_heads, int q_block, int page_size, float scale_log2,
-    int window, int* __restrict__ status) {
+    int window, int* __restrict__ status, int nsplit, float* __restrict__ part_o,
+    float2* __restrict__ part_ml) {
     static_assert(HD == 64, "one 128-byte swizzle row per key");
     rv_pdl_prologue();
     // blocks are handed out in the order x, then y: with the key/value head in x, all heads of a
     // request's longest block of query tokens start first, then all heads of the next longest
-    const int r = first_req + blockIdx.z, g = blockIdx.x;
+    // nsplit > 1: the key tiles of a block of query tokens are shared out over `nsplit` blocks
+    // (blockIdx.z = request * nsplit + part), each leaving its unnormalised O rows, offsets and
+    // sums in `part_o` / `part_ml` for paged_attention_prefill_merge_kernel
+    const int r_local = (int)blockIdx.z / nsplit, part = (int)blockIdx.z - r_local * nsplit;
+    const int r = first_req + r_local, g = blockIdx.x;
     const int clen = ctx_lens[r];
     const int qs = q_start[r];
     const int qlen = q_start[r + 1] - qs;
@@ -182,8 +187,11 @@ __global__ void __launch_bounds__(192, 3) paged_attention_prefill_tcgen05_kernel
     const int start = clen - qlen;                              // position of the portion's first token
     const int p_first = start + q0, p_last = p_first + n_tok - 1;
     const int key_lo = window > 0 ? max(0, p_first - window + 1) : 0;
-    const int t_lo = key_lo / AT_KEYS, t_hi = p_last / AT_KEYS;
-    const int n_tiles = t_hi - t_lo + 1;
+    const int t_all = key_lo / AT_KEYS, t_hi = p_last / AT_KEYS;
+    const int per_part = (t_hi - t_all + nsplit) / nsplit;        // ceil(tiles / nsplit)
+    const int t_lo = t_all + part * per_part;                      // this block's first tile
+    if (t_lo > t_hi) return;                                    // a part without tiles
+    const int n_tiles = min(t_hi, t_lo + per_part - 1) - t_lo + 1;
     const int page_shift = 31 - __clz(page_size);
     const int ppt = AT_KEYS >> page_shift;                      // pages per tile (1..16)
     const unsigned page_bytes = (unsigned)page_size * HD * 2u;
@@ -464,6 +472,22 @@ __global__ void __launch_bounds__(192, 3) paged_attention_prefill_tcgen05_kernel
         if (__all_sync(0xffffffffu, done && !failed)) {         // one answer per warp: the reads
                                                                 // below are warp-wide
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            if (nsplit > 1) {
+                // this part's rows as they stand: O unnormalised, the offset and the sum
+                const size_t slot = (((size_t)r_local * gridDim.y + blockIdx.y) * gridDim.x + g) * nsplit + part;
+                float* po = part_o + (slot * AT_ROWS + m) * HD;
+                if (row_ok) part_ml[slot * AT_ROWS + m] = make_float2(m_run, l_run);
+#pragma unroll
+                for (int c = 0; c < HD; c += 16) {
+                    float v[16];
+                    at_tmem_ld16(tmem_o + lane_base + (unsigned)c, v);
+                    if (row_ok) {
+#pragma unroll
+                        for (int j = 0; j < 16; j += 4)
+                            *(float4*)(po + c + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                    }
+                }
+            } else {
             const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
             bf16* dst = out + (size_t)(qs + q0 + tok) * num_heads * HD + (size_t)(g * G + head) * HD;
 #pragma unroll
@@ -481,6 +505,7 @@ __global__ void __launch_bounds__(192, 3) paged_attention_prefill_tcgen05_kernel
                     *(uint4*)(dst + c + 8) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
                 }
             }
+            }
         } else if (!failed) {
             failed = 1;
             atomicCAS(status, 0, 21);
@@ -492,6 +517,67 @@ __global__ void __launch_bounds__(192, 3) paged_attention_prefill_tcgen05_kernel
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
                      "r"(128u));
     }
+}
+
+// The parts of a block of query tokens put together, in order.  A thread owns four columns of
+// one row and requests every part's values before it uses any (one memory latency, however
+// many parts); 16 rows a block, so blockIdx.z = request * 8 + sixteen rows of the 128.  The
+// same arithmetic as the kernel above, so a part that had no tiles is skipped here too.
+#define AT_MAX_PARTS 16
+template <int HD>
+__global__ void __launch_bounds__(16 * (HD / 4)) paged_attention_prefill_merge_kernel(
+    const float* __restrict__ part_o, const float2* __restrict__ part_ml,
+    const int* __restrict__ q_start, const int* __restrict__ ctx_lens, bf16* __restrict__ out,
+    int first_req, int num_heads, int num_kv_heads, int q_block, int window, int nsplit) {
+    rv_pdl_prologue();
+    constexpr int CH = HD / 4;                                  // 4-column chunks of a row
+    const int r_local = (int)blockIdx.z / (AT_ROWS / 16), rows0 = ((int)blockIdx.z % (AT_ROWS / 16)) * 16;
+    const int r = first_req + r_local, g = blockIdx.x;
+    const int clen = ctx_lens[r];
+    const int qs = q_start[r];
+    const int qlen = q_start[r + 1] - qs;
+    const int nqb = (qlen + q_block - 1) / q_block;
+    if ((int)blockIdx.y >= nqb || clen == 0) return;
+    const int qb = nqb - 1 - blockIdx.y;
+    const int G = num_heads / num_kv_heads;
+    const int q0 = qb * q_block;
+    const int n_tok = min(q_block, qlen - q0);
+    const int p_first = clen - qlen + q0, p_last = p_first + n_tok - 1;
+    const int key_lo = window > 0 ? max(0, p_first - window + 1) : 0;
+    const int t_all = key_lo / AT_KEYS, t_hi = p_last / AT_KEYS;
+    const int per_part = (t_hi - t_all + nsplit) / nsplit;
+    const int m = rows0 + (int)threadIdx.x / CH, c = ((int)threadIdx.x % CH) * 4;
+    const int tok = m / G, head = m - tok * G;
+    if (tok >= n_tok) return;
+    const size_t slot0 = (((size_t)r_local * gridDim.y + blockIdx.y) * gridDim.x + g) * nsplit;
+    float2 ml[AT_MAX_PARTS];
+    float4 v[AT_MAX_PARTS];
+#pragma unroll
+    for (int p = 0; p < AT_MAX_PARTS; ++p) {
+        const bool there = p < nsplit && t_all + p * per_part <= t_hi;
+        ml[p] = there ? part_ml[(slot0 + p) * AT_ROWS + m] : make_float2(-INFINITY, 0.f);
+        v[p] = there ? *(const float4*)(part_o + ((slot0 + p) * AT_ROWS + m) * HD + c)
+                     : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    float M = -INFINITY;
+#pragma unroll
+    for (int p = 0; p < AT_MAX_PARTS; ++p)
+        if (ml[p].y > 0.f) M = fmaxf(M, ml[p].x);
+    float L = 0.f;
+    float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int p = 0; p < AT_MAX_PARTS; ++p) {
+        if (ml[p].y > 0.f) {                                    // something visible in this part
+            const float w = at_exp2(ml[p].x - M);
+            L += ml[p].y * w;
+            o.x += v[p].x * w; o.y += v[p].y * w; o.z += v[p].z * w; o.w += v[p].w * w;
+        }
+    }
+    const float inv = L > 0.f ? 1.f / L : 0.f;
+    bf16* dst = out + (size_t)(qs + q0 + tok) * num_heads * HD + (size_t)(g * G + head) * HD + c;
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(o.x * inv, o.y * inv);
+    const __nv_bfloat162 hi = __floats2bfloat162_rn(o.z * inv, o.w * inv);
+    *(uint2*)dst = make_uint2(*(const unsigned*)&lo, *(const unsigned*)&hi);
 }
 
 // ---- host side ----------------------------------------------------------------------------
@@ -534,13 +620,45 @@ static int at_map(CUtensorMap* map, const void* ptr, long long rows, int mid, lo
     return 0;
 }
 
-// Requests [first_req, first_req + n_reqs), the longest bringing max_q_len tokens; `q` is the
-// q|k|v buffer [n_tokens, q_stride] (the query heads first), `out` is [n_tokens, heads * 64].
+// A launch with fewer blocks than two an SM shares the key tiles of every block of query tokens
+// out over several blocks, so that a short portion at the end of a long context is not one long
+// chain of tiles on a few SMs (256 tokens at the end of 4,096: 64.7 -> 31.7 us; 512 at the end of
+// 2,048: 35.6 -> 31.6); the parts are put together by the merge kernel.  About two blocks an SM
+// in all (with three the blocks slow one another down as much as the sharing out gains: 1,024
+// tokens at the end of 4,096 78.7 -> 85.1 us), at most 16 parts: the scratch for the parts is bounded by the size below.
+#define AT_PART_BYTES ((size_t)AT_ROWS * (RV_HD * 4 + 8))
+extern "C" long long AT_SYM(rv_paged_attention_prefill_tcgen05_scratch_bytes)(int n_sms) {
+    return (long long)(6 * (size_t)(n_sms > 0 ? n_sms : 1) * AT_PART_BYTES);
+}
+
+static int at_parts(long long blocks, int max_ctx_len, int max_q_len, int n_sms, long long scratch_bytes) {
+    static const int forced = [] {
+        const char* e = getenv("RVLLM_PREFILL_SPLIT");
+        return e && *e ? atoi(e) : 0;
+    }();
+    const long long places = 2ll * n_sms;
+    int parts = forced > 0 ? forced : (int)((places + blocks / 2) / blocks);
+    // the tiles every block of query tokens has before its own: a whole prompt (none before it)
+    // is a triangle of mostly short blocks, which sharing out only burdens (1,000 tokens alone:
+    // 22.7 -> 29.2 us with two parts); four such tiles to a part at least
+    const int before = (max_ctx_len > max_q_len ? max_ctx_len - max_q_len : 0) / AT_KEYS;
+    if (forced <= 0 && parts > before / 4) parts = before / 4;
+    if (parts > AT_MAX_PARTS) parts = AT_MAX_PARTS;
+    while (parts > 1 && (blocks * parts > 3 * places ||
+                         (long long)(blocks * parts * AT_PART_BYTES) > scratch_bytes))
+        --parts;
+    return parts < 1 ? 1 : parts;
+}
+
+// Requests [first_req, first_req + n_reqs), the longest bringing max_q_len tokens and holding
+// max_ctx_len; `q` is the q|k|v buffer [n_tokens, q_stride] (the query heads first), `out` is
+// [n_tokens, heads * 64]; `scratch` (may be null: no sharing out) holds the parts.
 extern "C" int AT_SYM(rv_paged_attention_prefill_tcgen05)(
     const void* q, int q_stride, int n_tokens, const void* k_cache, const void* v_cache,
     long long total_slots, const int* block_table, int max_blocks, const int* q_start,
-    const int* ctx_lens, void* out, int first_req, int n_reqs, int max_q_len, int num_heads,
-    int num_kv_heads, int page_size, float scale, int window, int* status, void* stream) {
+    const int* ctx_lens, void* out, int first_req, int n_reqs, int max_q_len, int max_ctx_len,
+    int num_heads, int num_kv_heads, int page_size, float scale, int window, int* status,
+    void* scratch, long long scratch_bytes, int n_sms, void* stream) {
     if (n_reqs == 0 || max_q_len == 0) return 0;
     if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads || n_reqs < 0)
         return at_fail("paged_attention_prefill_tcgen05: bad head counts");
@@ -570,11 +688,25 @@ extern "C" int AT_SYM(rv_paged_attention_prefill_tcgen05)(
         configured = true;
     }
     const int nqb = (max_q_len + q_block - 1) / q_block;
-    rv_launch(paged_attention_prefill_tcgen05_kernel<RV_HD>, dim3(num_kv_heads, nqb, n_reqs),
+    const long long blocks = (long long)num_kv_heads * nqb * n_reqs;
+    const int parts = scratch && n_sms > 0 ? at_parts(blocks, max_ctx_len, max_q_len, n_sms, scratch_bytes) : 1;
+    if ((long long)n_reqs * (parts > AT_ROWS / 16 ? parts : AT_ROWS / 16) > 65535)
+        return at_fail("paged_attention_prefill_tcgen05: too many requests");
+    float* part_o = (float*)scratch;
+    float2* part_ml = (float2*)((char*)scratch + (size_t)blocks * parts * AT_ROWS * RV_HD * 4);
+    rv_launch(paged_attention_prefill_tcgen05_kernel<RV_HD>, dim3(num_kv_heads, nqb, n_reqs * parts),
               dim3(192), smem, (cudaStream_t)stream, map_q, map_k, map_v, block_table, max_blocks,
               q_start, ctx_lens, (bf16*)out, first_req, num_heads, num_kv_heads, q_block, page_size,
-              scale * 1.4426950408889634f, window, status);
+              scale * 1.4426950408889634f, window, status, parts, part_o, part_ml);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return at_fail(cudaGetErrorString(e));
+    if (parts > 1) {
+        rv_launch(paged_attention_prefill_merge_kernel<RV_HD>,
+                  dim3(num_kv_heads, nqb, n_reqs * (AT_ROWS / 16)), dim3(16 * (RV_HD / 4)), 0,
+                  (cudaStream_t)stream, (const float*)part_o, (const float2*)part_ml,
+                  q_start, ctx_lens, (bf16*)out, first_req, num_heads, num_kv_heads, q_block, window, parts);
+        e = cudaGetLastError();
+        if (e != cudaSuccess) return at_fail(cudaGetErrorString(e));
+    }
     return 0;
 }

@@ -208,6 +208,9 @@ class _Subset(_InFlight):
         return [all_tokens[i] for i in self._keep]
 
 
+_FROZEN_AT_IMPORT = gc.get_freeze_count()
+
+
 @contextlib.contextmanager
 def settled_heap():
     """Keep Python's cyclic garbage collector off what is on the heap already.
@@ -218,15 +221,21 @@ def settled_heap():
     a workload's time.  On entry garbage is collected once and what remains is moved to the
     permanent generation (`gc.freeze`), which later passes skip; on exit it is moved back.
     Objects made inside are collected as usual.  RVLLM_GC_FREEZE=0 turns it off."""
-    if os.environ.get("RVLLM_GC_FREEZE", "1") == "0" or gc.get_freeze_count() > 0:
-        yield                      # switched off, or the caller has frozen the heap already:
-        return                     # `gc.unfreeze` below would thaw their objects too
+    if os.environ.get("RVLLM_GC_FREEZE", "1") == "0":
+        yield
+        return
+    # A permanent generation that has grown since this module was imported is somebody else's
+    # (a caller who froze their heap): it is added to and then left as it is, because
+    # `gc.unfreeze` would thaw their objects too.  (The interpreter itself starts with a few
+    # hundred objects there.)
+    thaw = gc.get_freeze_count() <= _FROZEN_AT_IMPORT
     gc.collect()
     gc.freeze()
     try:
         yield
     finally:
-        gc.unfreeze()
+        if thaw:
+            gc.unfreeze()
 
 
 def run(runner, requests: Sequence[Request], config: SchedulerConfig, context_length: int,

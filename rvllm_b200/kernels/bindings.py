@@ -323,8 +323,9 @@ class CudaOps:
         """Bytes of split-KV scratch the decode attention kernels need at most for
         `n_reqs` single-token requests of up to `max_ctx_len` cached tokens (with the
         smallest split any of them uses, 128 keys)."""
-        return int(self.lib.rv_paged_attention_decode_scratch_bytes(
+        decode = int(self.lib.rv_paged_attention_decode_scratch_bytes(
             c_int(n_reqs), c_int(num_heads), c_int(head_dim), c_int(2 * max_ctx_len)))
+        return max(decode, self._prefill_scratch_bytes(head_dim))
 
     def reserve_scratch(self, nbytes: int, device) -> None:
         """Size the scratch before any launch sequence is captured, so that it does not
@@ -374,17 +375,33 @@ class CudaOps:
         lib = self._attn5_lib(head_dim)
         nd = ctx.n_decode
         fn = getattr(lib, f"rv_paged_attention_prefill_tcgen05_hd{head_dim}")
+        # scratch for the parts of a launch too small to fill the GPU (the kernel shares the key
+        # tiles of its blocks out); never made or grown inside a stream capture
+        need = self._prefill_scratch_bytes(head_dim)
+        scratch = self._scratch.get(str(qkv.device))
+        if scratch is None or scratch.numel() < need:
+            scratch = (None if torch.cuda.is_current_stream_capturing()
+                       else self._scratch_buffer(need, qkv.device))
         rc = fn(_ptr(qkv), c_int(qkv.shape[1]), c_int(qkv.shape[0]), _ptr(k_cache), _ptr(v_cache),
                 c_longlong(k_cache.shape[0] * k_cache.shape[1]), _ptr(group.block_table),
                 c_int(group.max_blocks), _ptr(ctx.q_start), _ptr(ctx.ctx_lens), _ptr(out),
-                c_int(nd), c_int(ctx.n_reqs - nd), c_int(ctx.max_q_len), c_int(num_heads),
-                c_int(num_kv_heads), c_int(group.page_size), c_float(scale),
+                c_int(nd), c_int(ctx.n_reqs - nd), c_int(ctx.max_q_len), c_int(ctx.max_ctx_len),
+                c_int(num_heads), c_int(num_kv_heads), c_int(group.page_size), c_float(scale),
                 c_int(window if window else 0), _ptr(self._gemm_status(qkv.device)),
-                self._stream())
+                _ptr(scratch), c_longlong(scratch.numel() if scratch is not None else 0),
+                c_int(self._sm_count), self._stream())
         self.launches += 1
         if rc != 0:
             msg = getattr(lib, f"rv_attention_tcgen05_last_error_hd{head_dim}")().decode()
             raise KernelError(f"paged_attention_prefill_tcgen05: {msg}")
+
+    def _prefill_scratch_bytes(self, head_dim: int) -> int:
+        """What the tcgen05 prefill attention may use for the parts of shared-out blocks."""
+        if head_dim != 64 or self.prefill_attention not in ("auto", "tcgen05"):
+            return 0
+        # rv_paged_attention_prefill_tcgen05_scratch_bytes: six parts an SM, each 128 rows of
+        # 64 float32 values, an offset and a sum (the kernel fits its parts to what it is given)
+        return 6 * self._sm_count * 128 * (64 * 4 + 8)
 
     def _check_attn(self, lib, head_dim: int, rc: int, what: str) -> None:
         self.launches += 1

@@ -601,6 +601,12 @@ PREFILL_CASES = [
     ([257], [257], 1, 1, 64, 16, None),
     ([20, 9], [90, 9], 32, 1, 64, 16, None),      # 4 query tokens per block of 128 rows
     ([15], [75], 7, 1, 64, 8, None),              # 18 tokens x 7 heads = 126 rows, 2 unused
+    # few blocks and long contexts: the key tiles of a block are shared out over several blocks
+    # and merged (4 parts; 3 parts of which the shorter request fills only some; with a window)
+    ([40], [2000], 8, 2, 64, 16, None),
+    ([100, 7], [3000, 900], 4, 4, 64, 32, None),
+    ([64], [1800], 8, 2, 64, 16, 700),
+    ([30], [8100], 8, 2, 64, 16, None),           # 16 parts
 ]
 
 

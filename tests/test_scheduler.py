@@ -184,19 +184,23 @@ def test_seeded_sampling_counts_per_request():
 
 def test_settled_heap_freezes_and_gives_back(monkeypatch):
     """Inside, what was on the heap is in the permanent generation (the collector's passes skip
-    it); afterwards nothing is left there; RVLLM_GC_FREEZE=0 leaves the collector alone."""
+    it); afterwards it is back; a heap the caller froze is added to and kept; RVLLM_GC_FREEZE=0
+    leaves the collector alone."""
     import gc
 
     from rvllm_b200.engine import settled_heap
+    from rvllm_b200.engine.engine import _FROZEN_AT_IMPORT
     gc.unfreeze()
+    assert gc.get_freeze_count() <= _FROZEN_AT_IMPORT
     with settled_heap():
-        assert gc.get_freeze_count() > 0
+        assert gc.get_freeze_count() > 1000
     assert gc.get_freeze_count() == 0
-    gc.freeze()                               # a caller's own freeze is left as it is
+    gc.freeze()                               # a caller's own freeze is added to and kept
     mine = gc.get_freeze_count()
+    assert mine > _FROZEN_AT_IMPORT
     with settled_heap():
-        pass
-    assert gc.get_freeze_count() >= mine > 0
+        assert gc.get_freeze_count() >= mine
+    assert gc.get_freeze_count() >= mine
     gc.unfreeze()
     monkeypatch.setenv("RVLLM_GC_FREEZE", "0")
     with settled_heap():
