@@ -78,6 +78,7 @@ class CudaOps:
         self._gemm_state = {}
         self._tiled = {}
         self.gemm_tiled = os.environ.get("RVLLM_GEMM_TILED", "1") != "0"
+        self.gemm_row_pad = int(os.environ.get("RVLLM_GEMM_ROW_PAD", "64"))
         # q/k norm + rotation + cache write inside the q|k|v product's epilogue (few bfloat16
         # tokens, head size 64); "0": always the separate kernel
         self.fuse_qkv_rope = os.environ.get("RVLLM_FUSE_QKV_ROPE", "1") == "1"
@@ -97,6 +98,12 @@ class CudaOps:
 
     @staticmethod
     def _stream() -> c_void_p:
+        # the current stream of the current device; the raw query is a fraction of a microsecond
+        # where `torch.cuda.current_stream()` builds a Python object in some 15 (and a step of a
+        # small model makes some 140 launches)
+        raw = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+        if raw is not None:
+            return c_void_p(raw(torch._C._cuda_getDevice()))
         return c_void_p(torch.cuda.current_stream().cuda_stream)
 
     @staticmethod
@@ -266,15 +273,45 @@ class CudaOps:
             return torch.empty((0, w.shape[0]), dtype=out_dtype, device=x.device)
         if self._small_product(x, w, out_dtype):
             y = self.linear_tcgen05(x, w, out_dtype)
-        elif out_dtype == x.dtype:
-            y = torch.mm(x, w.t())
-        elif x.dtype == torch.bfloat16 and out_dtype == torch.float32:
-            y = torch.mm(x, w.t(), out_dtype=torch.float32)
         else:
-            y = torch.mm(x, w.t()).to(out_dtype)
+            # The library chooses an algorithm per shape, and a shape it has not met costs it
+            # some 70 us on the host: a prompt portion of 301 tokens, then 302, ... would pay
+            # that in every product of every step.  So it is shown row counts in multiples of
+            # 64 (RVLLM_GEMM_ROW_PAD): the rows beyond the real ones are whatever the buffer
+            # holds (`new_rows` leaves room for them) and their results are dropped.
+            m = x.shape[0]
+            xp = self._padded_rows(x)
+            if out_dtype == x.dtype:
+                y = torch.mm(xp, w.t())
+            elif x.dtype == torch.bfloat16 and out_dtype == torch.float32:
+                y = torch.mm(xp, w.t(), out_dtype=torch.float32)
+            else:
+                y = torch.mm(xp, w.t()).to(out_dtype)
+            if y.shape[0] != m:
+                y = y[:m]
         if bias is not None:
             self.add_bias(y, bias)
         return y
+
+    def new_rows(self, n, width, dtype, device):
+        """An uninitialised [n, width] buffer for activation rows whose storage is a multiple
+        of the row padding long, so that a library product can take it as it is."""
+        pad = self.gemm_row_pad
+        if pad <= 1 or n % pad == 0:
+            return torch.empty((n, width), dtype=dtype, device=device)
+        return torch.empty((-(-n // pad) * pad, width), dtype=dtype, device=device)[:n]
+
+    def _padded_rows(self, x):
+        pad = self.gemm_row_pad
+        m, k = x.shape
+        if pad <= 1 or m % pad == 0 or not x.is_contiguous():
+            return x
+        mp = -(-m // pad) * pad
+        if x.storage_offset() == 0 and x.untyped_storage().nbytes() >= mp * k * x.element_size():
+            return x.as_strided((mp, k), (k, 1))          # the buffer has the room (`new_rows`)
+        xp = torch.empty((mp, k), dtype=x.dtype, device=x.device)
+        xp[:m].copy_(x)
+        return xp
 
     def add_bias(self, x, bias):
         self._need(x, "add_bias input")

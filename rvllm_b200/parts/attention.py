@@ -98,8 +98,7 @@ class Attention(Mixer):
             self.q_norm, self.k_norm if owns else None, s.qk_norm.eps if s.qk_norm else 0.0,
             self.position.rotation_table(), ctx.positions, group.slot_mapping,
             cache.k if owns else None, cache.v if owns else None, out_dtype=self.dtype)
-        out = torch.empty((normed.shape[0], s.num_heads * s.head_dim), dtype=self.dtype,
-                          device=normed.device)
+        out = self.ops.new_rows(normed.shape[0], s.num_heads * s.head_dim, self.dtype, normed.device)
         self.ops.paged_attention(qkv, s.num_heads, s.num_kv_heads, s.head_dim,
                                  cache.k, cache.v, ctx, group, self.scale, s.window, out)
         return self.ops.linear(out, self.w_out, out_dtype=self.dtype)

@@ -35,8 +35,7 @@ class SwiGLU(FeedForward):
 
     def forward(self, normed, ctx):
         gate_up = self.ops.linear(normed, self.gate_up, out_dtype=self.dtype)
-        act = torch.empty((normed.shape[0], self.spec.ffn_dim), dtype=self.dtype,
-                          device=normed.device)
+        act = self.ops.new_rows(normed.shape[0], self.spec.ffn_dim, self.dtype, normed.device)
         self.ops.swiglu(gate_up, act)
         return self.ops.linear(act, self.down, out_dtype=self.dtype)
 

@@ -29,13 +29,13 @@ class RMSNorm(Norm):
 
     def add_norm(self, resid, delta, ctx, rows=None):
         n = resid.shape[0] if rows is None else rows.shape[0]
-        out = torch.empty((n, self.spec.size), dtype=self.dtype, device=resid.device)
+        out = self.ops.new_rows(n, self.spec.size, self.dtype, resid.device)
         self.ops.add_rmsnorm(resid, delta, self.weight, self.spec.eps, out, rows)
         return out
 
 
     def norm(self, x, ctx):
-        out = torch.empty((x.shape[0], self.spec.size), dtype=self.dtype, device=x.device)
+        out = self.ops.new_rows(x.shape[0], self.spec.size, self.dtype, x.device)
         self.ops.add_rmsnorm(None, x, self.weight, self.spec.eps, out, None)
         return out
 

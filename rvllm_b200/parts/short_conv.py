@@ -69,8 +69,7 @@ class ShortConv(Mixer):
         if cache is not None and not cache.owns:
             raise ValueError("short_conv: a convolution state cannot be shared between calls")
         proj = self.ops.linear(normed, self.w_in, out_dtype=self.dtype)
-        y = torch.empty((normed.shape[0], self.spec.hidden), dtype=self.dtype,
-                        device=normed.device)
+        y = self.ops.new_rows(normed.shape[0], self.spec.hidden, self.dtype, normed.device)
         self.ops.short_conv(proj, self.filter, self.b_in, self.b_conv,
                             cache.state if cache is not None else None, ctx, y)
         out = self.ops.linear(y, self.w_out, out_dtype=self.dtype)

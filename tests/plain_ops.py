@@ -50,6 +50,9 @@ class PlainOps:
             y = y + _f(bias)
         return y.to(out_dtype or x.dtype)
 
+    def new_rows(self, n, width, dtype, device):
+        return torch.empty((n, width), dtype=dtype, device=device)
+
     def linear_qk_norm_rope_write(self, x, w_qkv, num_heads, num_kv_heads, head_dim, q_weight,
                                   k_weight, eps, table, positions, slot_mapping, k_cache, v_cache,
                                   out_dtype=None):
