@@ -5,6 +5,12 @@ the model it sits in.  A mixer tells the cache manager what it has to remember
 through `cache_need`: keys and values per token in pages (`PagedNeed`), a record of
 fixed size per request (`StateNeed`), or nothing.
 
+Buffers for activation rows that a matrix product will read (`[tokens, width]` outputs of
+a norm, an activation, a mixer's inner stage) come from `ops.new_rows(n, width, dtype,
+device)` rather than `torch.empty`: the kernel set may leave room behind them so that the
+matrix library is shown row counts it has met before.  Any tensor still works as a
+product's input; it is then copied once.
+
 Adding a part: subclass the interface, give `params` and (for a mixer) `cache_need`,
 and call the matching `register_*` with the `kind` string its spec carries.  Nothing
 else in the package has to change.
