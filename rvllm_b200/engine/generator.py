@@ -90,10 +90,26 @@ class Generator:
             return list(self.tokenizer.encode(prompt).ids)
         return [int(t) for t in prompt]
 
-    def _runner_for(self, block_size: int, num_blocks: int, slots: int) -> ModelRunner:
+    def _runner_for(self, block_size: int, num_blocks: int, slots: int,
+                    exact: bool = True) -> ModelRunner:
+        """The runner with a pool of `num_blocks` pages and `slots` state slots.  `exact`
+        False (the pool was sized for this call's requests, not asked for by the caller): a
+        runner from an earlier call whose pool is at least as large is used again, with its
+        captured launch sequences, instead of a new pool and new captures for every call."""
+        if not exact:
+            slots = max(slots, 8)             # state slots are small; fewer rebuilds for small batches
+        have = self._runner
+        if have is not None and not exact and self._runner_key[0] == block_size \
+                and have.cache.num_pages >= num_blocks and have.cache.max_requests >= slots:
+            return have
         key = (block_size, num_blocks, slots)
         if self._runner_key != key:
-            self._runner = None
+            if not exact and have is not None and self._runner_key[0] == block_size:
+                # grow by half at least, so that calls of slowly growing size do not each rebuild
+                num_blocks = max(num_blocks, have.cache.num_pages + have.cache.num_pages // 2)
+                slots = max(slots, have.cache.max_requests)
+                key = (block_size, num_blocks, slots)
+            self._runner = have = None
             cache = make_cache(self.model, block_size, num_blocks, slots)
             self._runner = ModelRunner(self.model, cache, self.ops, use_graphs=graphs_default())
             self._runner_key = key
@@ -135,7 +151,8 @@ class Generator:
             num_blocks = sum(max(1, -(-min(len(p) + opts.max_tokens, context) // bs))
                              for p in prompts)
         slots = min(len(prompts), opts.max_running) if opts.max_running else len(prompts)
-        runner = self._runner_for(bs, num_blocks, max(1, slots))
+        runner = self._runner_for(bs, num_blocks, max(1, slots), exact=opts.num_blocks is not None)
+        num_blocks = runner.cache.num_pages
         cfg = SchedulerConfig(block_size=bs, num_blocks=num_blocks,
                               max_running=opts.max_running or (1 << 30),
                               max_num_batched_tokens=opts.max_batched_tokens,

@@ -43,6 +43,30 @@ def test_greedy_tiny_a_workload(folders):
                                                     stop_tokens=[])) == want[1]
 
 
+def test_generator_keeps_its_pool_between_calls(folders):
+    """A pool sized for a call's own requests is used again by a later call that fits into it
+    (no new cache, no new captures); a larger call grows it; a pool the caller asks for by
+    size is made exactly; the tokens are the plain implementation's every time."""
+    from rvllm_b200 import GenerateOptions, Generator
+    plain = PlainModel(folders["A"])
+    rng = random.Random(3)
+    prompts = [[rng.randrange(512) for _ in range(n)] for n in (40, 9, 23, 60)]
+    want = [plain.greedy(p, 8) for p in prompts]
+    gen = Generator.load(folders["A"], dtype="float32")
+    opts = GenerateOptions(max_tokens=8, block_size=8, stop_tokens=[])
+    assert gen.complete(prompts[3], opts) == want[3]            # 9 pages of 8
+    first = gen._runner
+    assert gen.complete(prompts[1], opts) == want[1] and gen._runner is first
+    assert gen.complete_batch(prompts[1:3], opts) == want[1:3] and gen._runner is first   # 7 pages
+    assert gen.complete_batch(prompts, opts) == want            # 22 pages: a new pool
+    grown = gen._runner
+    assert grown is not first and grown.cache.num_pages >= 22
+    assert gen.complete(prompts[3], opts) == want[3] and gen._runner is grown
+    exact = GenerateOptions(max_tokens=8, block_size=8, stop_tokens=[], num_blocks=11)
+    assert gen.complete(prompts[2], exact) == want[2]
+    assert gen._runner.cache.num_pages == 11
+
+
 def test_stop_token_ends_and_is_stripped(folders):
     from rvllm_b200 import GenerateOptions, Generator
     plain = PlainModel(folders["A"])
