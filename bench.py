@@ -641,6 +641,7 @@ def run_workload(name, verbose=False):
             engine.add_request(Request(i, ids, w["new"], (), SamplingParams(),
                                        arrival_step=i * w["arrival_gap"]))
         steps0, graph0 = runner.steps, runner.graph_steps
+        captures0 = runner.captures
         marks, host = [], []
         out_tokens = 0
         torch.cuda.synchronize()
@@ -660,6 +661,11 @@ def run_workload(name, verbose=False):
         if not timed:
             return None
         device = [a.elapsed_time(b) for a, b in marks]
+        if os.environ.get("RVLLM_BENCH_STEPS"):              # the slowest steps, for a look
+            worst = sorted(range(len(device)), key=lambda i: -host[i])[:12]
+            print("slowest steps (index, host ms, device ms):",
+                  [(i, round(1e3 * host[i], 2), round(device[i], 2)) for i in sorted(worst)],
+                  file=sys.stderr)
         st = engine.scheduler.stats
         n_steps = runner.steps - steps0
         busy = sum(device) / 1e3
@@ -675,6 +681,7 @@ def run_workload(name, verbose=False):
             "host_ms_per_step": round(1e3 * sum(host) / len(host), 3),
             "device_ms_per_step": round(sum(device) / len(device), 3),
             "gpu_idle_frac": round(max(0.0, 1.0 - busy / wall), 3),
+            "graphs_captured_meanwhile": runner.captures - captures0,
         }
 
     one_run(False)

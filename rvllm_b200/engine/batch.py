@@ -61,6 +61,7 @@ class StepContext:
     ctx_lens_host: List[int] = field(default_factory=list)
     max_q_len: int = 0
     max_ctx_len: int = 0
+    n_wanted: int = 0               # logit rows that were asked for (the first ones)
 
 
 def _align(n: int) -> int:
@@ -88,14 +89,21 @@ class BatchBuilder:
         return self._host, self._dev
 
     def build(self, entries: Sequence[StepEntry], pad_reqs: int = 0,
-              pad_blocks: int = 0, buffers=None, row_order: Optional[Sequence[int]] = None
-              ) -> StepContext:
+              pad_blocks: int = 0, buffers=None, row_order: Optional[Sequence[int]] = None,
+              pad_mixed: Optional[Sequence[int]] = None) -> StepContext:
         """`entries` must already be ordered single-token requests first.  `pad_reqs` /
         `pad_blocks` pad the request count (with empty requests that every kernel
         skips) and the block-table width, so that a captured launch sequence sees the
         same addresses and sizes; `buffers` = (host, device) to fill instead of the
         builder's own.  `row_order`: the entries' indices in the order in which their wanted
-        rows are to come out (the callers' order, when the entries were reordered)."""
+        rows are to come out (the callers' order, when the entries were reordered).
+
+        `pad_mixed` = (D, P, T, W) pads a step of any mixture to fixed sizes: requests
+        [0, D) bring one token each (the real single-token entries, then empty ones), requests
+        [D, D + P) are the prompt portions (the real ones, then empty ones without tokens; the
+        last one owns the tokens that fill the batch up to T and has no context, so every
+        kernel computes nothing for them or something nobody reads), and W logit rows come out
+        (the wanted ones first)."""
         cache = self.cache
         ps = cache.page_size
         q_lens = [len(e.tokens) for e in entries]
@@ -108,11 +116,32 @@ class BatchBuilder:
             raise ValueError("single-token entries must come first")
         r_real = len(entries)
         n_real = sum(q_lens)
-        pad = max(0, pad_reqs - r_real)
-        if pad and n_decode != r_real:
-            raise ValueError("padding is for steps of single tokens only")
-        R = r_real + pad
-        N = n_real + pad
+        n_want = sum(len(e.want) for e in entries)
+        if pad_mixed is not None:
+            D, P, T, W = (int(v) for v in pad_mixed)
+            n_prefill = r_real - n_decode
+            tail = T - D - (n_real - n_decode)           # tokens that only fill the batch
+            if pad_reqs or n_decode > D or n_prefill > P or tail < 0 or n_want > W or \
+                    (tail > 0 and n_prefill >= P):
+                raise ValueError("the step does not fit the padded sizes")
+            R, N, M = D + P, T, W
+            req_of = list(range(n_decode)) + [D + j for j in range(n_prefill)]
+            q_all = [1] * D + q_lens[n_decode:] + [0] * (P - n_prefill)
+            if tail:
+                q_all[-1] = tail
+            dec_pad = D
+        else:
+            pad = max(0, pad_reqs - r_real)
+            if pad and n_decode != r_real:
+                raise ValueError("padding is for steps of single tokens only")
+            R = r_real + pad
+            N = n_real + pad
+            # a padded (replayed) step produces the logits of every row, padding included, so
+            # that the captured launch sizes do not depend on how many requests are real
+            M = N if pad_reqs else n_want
+            req_of = list(range(r_real))
+            q_all = q_lens + [1] * pad
+            dec_pad = n_decode + pad
         rcs = [cache.requests[e.req] for e in entries]
         starts = [rc.computed for rc in rcs]
         ctx = [s + q for s, q in zip(starts, q_lens)]
@@ -124,9 +153,6 @@ class BatchBuilder:
         for gi in range(n_groups):
             mb = max([-(-c // ps) for c in ctx] + [1])
             max_blocks.append(max(mb, pad_blocks))
-        # a padded (replayed) step produces the logits of every row, padding included, so
-        # that the captured launch sizes do not depend on how many requests are real
-        M = N if pad_reqs else sum(len(e.want) for e in entries)
 
         # layout, in int32 words
         off = {}
@@ -153,31 +179,30 @@ class BatchBuilder:
             return h[a:a + n]
 
         q_start = np.zeros(R + 1, dtype=np.int64)
-        q_start[1:r_real + 1] = np.cumsum(q_lens)
-        if pad:
-            q_start[r_real + 1:] = n_real + np.arange(1, pad + 1)
+        q_start[1:] = np.cumsum(q_all)
         view("q_start")[:] = q_start
+        first = [int(q_start[r]) for r in req_of]        # each entry's first token
         tok = view("token_ids")
         pos = view("positions")
         treq = view("token_req")
-        tok[n_real:] = 0
-        pos[n_real:] = 0
+        tok[:] = 0
+        pos[:] = 0
+        treq[:] = np.repeat(np.arange(R), q_all)          # empty requests' tokens included
         if n_decode == r_real:                       # single tokens only: no per-request numpy
             tok[:r_real] = [e.tokens[0] for e in entries]
             pos[:r_real] = starts
-            treq[:r_real] = range(r_real)
         else:
-            for i, (e, s, q) in enumerate(zip(entries, starts, q_lens)):
-                a = int(q_start[i])
+            for a, e, s, q in zip(first, entries, starts, q_lens):
                 tok[a:a + q] = np.asarray(e.tokens, dtype=np.int64)
                 pos[a:a + q] = np.arange(s, s + q)
-                treq[a:a + q] = i
-        if pad:
-            treq[n_real:] = np.arange(r_real, R)
-        cl = view("ctx_lens"); cl[:r_real] = ctx; cl[r_real:] = 0
-        sp = view("start_pos"); sp[:r_real] = starts; sp[r_real:] = 0
-        ss = view("state_slot"); ss[:r_real] = [rc.slot for rc in rcs]; ss[r_real:] = -1
+        cl = view("ctx_lens"); cl[:] = 0
+        sp = view("start_pos"); sp[:] = 0
+        ss = view("state_slot"); ss[:] = -1
+        cl[req_of] = ctx
+        sp[req_of] = starts
+        ss[req_of] = [rc.slot for rc in rcs]
         rows = view("logit_rows")
+        rows[:] = 0
         k = 0
         if pad_reqs:
             rows[:] = np.arange(N)
@@ -188,19 +213,18 @@ class BatchBuilder:
                 if not 0 <= w < q_lens[i]:
                     raise ValueError(f"request {e.req!r}: wanted place {w} is outside "
                                      f"its {q_lens[i]} tokens")
-                rows[k] = int(q_start[i]) + w
+                rows[k] = first[i] + w
                 k += 1
         for gi in range(n_groups):
             mb = max_blocks[gi]
             table = view(f"table{gi}").reshape(R, mb)
             table[:] = -1
             slots = view(f"slot{gi}")
-            slots[n_real:] = -1
-            for i, (rc, s, q) in enumerate(zip(rcs, starts, q_lens)):
+            slots[:] = -1
+            for r, a, rc, s, q, c in zip(req_of, first, rcs, starts, q_lens, ctx):
                 t = rc.tables[gi].view()
-                nb = -(-ctx[i] // ps)
-                table[i, :nb] = t[:nb]
-                a = int(q_start[i])
+                nb = -(-c // ps)
+                table[r, :nb] = t[:nb]
                 if q == 1:
                     page = int(t[s // ps])
                     if page < 0:
@@ -229,11 +253,14 @@ class BatchBuilder:
                 block_table=dview(f"table{gi}").view(R, max_blocks[gi]),
                 slot_mapping=dview(f"slot{gi}"), max_blocks=max_blocks[gi],
                 page_size=ps, window=grp.need.window))
+        ctx_all = [0] * R
+        for r, c in zip(req_of, ctx):
+            ctx_all[r] = c
         return StepContext(
-            ops=self.ops, n_tokens=N, n_reqs=R, n_decode=n_decode + pad,
+            ops=self.ops, n_tokens=N, n_reqs=R, n_decode=dec_pad,
             token_ids=dview("token_ids"), positions=dview("positions"),
             token_req=dview("token_req"), q_start=dview("q_start"),
             ctx_lens=dview("ctx_lens"), start_pos=dview("start_pos"),
             state_slot=dview("state_slot"), logit_rows=dview("logit_rows"),
-            groups=groups, q_lens=q_lens + [1] * pad, ctx_lens_host=ctx + [0] * pad,
-            max_q_len=max(q_lens + [1]), max_ctx_len=max(ctx + [0]))
+            groups=groups, q_lens=list(q_all), ctx_lens_host=ctx_all,
+            max_q_len=max(q_all + [1]), max_ctx_len=max(ctx + [0]), n_wanted=k)

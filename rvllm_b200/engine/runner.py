@@ -16,6 +16,7 @@ from __future__ import annotations
 from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
 import gc
+import os
 import weakref
 
 import torch
@@ -37,8 +38,12 @@ class ModelRunner:
         self._shape_graphs: Dict[tuple, "_ShapeGraph"] = {}
         self._seen_shapes = set()
         self.max_shape_graphs = 16
+        self._mixed_graphs: Dict[tuple, "_MixedGraph"] = {}
+        self.max_mixed_graphs = int(os.environ.get("RVLLM_MIXED_GRAPHS", "24"))
         self.steps = 0
         self.graph_steps = 0
+        self.captures = 0                # launch sequences captured so far
+        self._graph_pool = None
         self.capture_failures = 0
         self._reserve_workspace()
 
@@ -61,6 +66,12 @@ class ModelRunner:
             m = spec.layers[call.layer].mixer
             need = max(need, mixer_class(m.kind).workspace_bytes(m, self.ops, requests, context))
         reserve(need, self.device)
+
+    def graph_pool(self):
+        """The memory pool that this runner's captured launch sequences share."""
+        if self._graph_pool is None:
+            self._graph_pool = torch.cuda.graph_pool_handle()
+        return self._graph_pool
 
     # ---- requests ----------------------------------------------------------------
 
@@ -121,13 +132,83 @@ class ModelRunner:
         if self.use_graphs and all(len(e.tokens) == 1 for e in ordered):
             return self._run_graph(ordered, device_tokens)
         if self.use_graphs and device_tokens is None:
-            logits = self._run_repeated_shape(ordered, row_order)
+            logits = self._run_padded_mixture(ordered, row_order)
+            if logits is None:
+                logits = self._run_repeated_shape(ordered, row_order)
             if logits is not None:
                 return logits
         ctx = self.builder.build(ordered, row_order=row_order)
         if device_tokens is not None:
             ctx.token_ids[:len(ordered)].copy_(device_tokens)
         return self.model.forward(ctx, self.cache.views())
+
+    def _run_padded_mixture(self, ordered: List[StepEntry], row_order=None) -> Optional[torch.Tensor]:
+        """Steps with prompt portions, padded to sizes that come again: D single-token
+        requests (a power of two), P prompt portions (a power of two, one more than there
+        are), T tokens in all (a multiple of 64, of 128 above 512, of 256 above 2,048) and a
+        block-table width as in single-token steps.  The second step that pads to the same
+        sizes is captured, and every later one replayed, whatever the portions' lengths and
+        the requests are: in live traffic exact shapes hardly ever come twice, and a step of
+        a small model launched kernel by kernel waits for the host (about 1.8 ms for some 140
+        launches).  Returns None when this step has to go another way."""
+        if self.max_mixed_graphs <= 0:
+            return None
+        n_decode = 0
+        while n_decode < len(ordered) and len(ordered[n_decode].tokens) == 1:
+            n_decode += 1
+        n_prefill = len(ordered) - n_decode
+        D = 0 if n_decode == 0 else 1 << (n_decode - 1).bit_length()
+        P = 1 << n_prefill.bit_length()                  # a power of two above n_prefill
+        tokens = D + sum(len(e.tokens) for e in ordered[n_decode:])
+        gran = 64 if tokens <= 512 else (128 if tokens <= 2048 else 256)
+        T = -(-tokens // gran) * gran
+        W = D + P
+        if sum(len(e.want) for e in ordered) > W:
+            return None
+        ps = self.cache.page_size
+        ctx_max = max(self.cache.requests[e.req].computed + len(e.tokens) for e in ordered)
+        blocks = -(-ctx_max // ps)
+        block_bucket = max(16, 1 << (blocks - 1).bit_length())
+        key = (D, P, T, block_bucket)
+        g = self._mixed_graphs.get(key)
+        if g is None:
+            seen = ("mixed",) + key
+            first_time = seen not in self._seen_shapes
+            if first_time:
+                if len(self._seen_shapes) > 4096:
+                    self._seen_shapes.clear()
+                self._seen_shapes.add(seen)
+            if first_time or len(self._mixed_graphs) >= self.max_mixed_graphs:
+                return self._padded_eagerly(ordered, row_order, key)
+            g = _MixedGraph(self, key)
+            self._mixed_graphs[key] = g
+        if g.broken:
+            return self._padded_eagerly(ordered, row_order, key)
+        try:
+            logits = g.run(ordered, row_order)
+        except RuntimeError as e:
+            if g.graph is not None and not g.capturing:
+                raise
+            g.broken = True
+            g.graph = None
+            self.capture_failures += 1
+            import warnings
+            warnings.warn(f"capturing a graph for steps padded to {T} tokens failed ({e}); "
+                          f"running such steps without it")
+            return None
+        self.graph_steps += 1
+        return logits
+
+    def _padded_eagerly(self, ordered, row_order, key) -> torch.Tensor:
+        """The step in the padded layout, launched kernel by kernel: the same kernels on the
+        same sizes as the replayed launch sequence of these sizes, so a position's logits do
+        not depend on whether its step had been captured yet."""
+        D, P, T, block_bucket = key
+        ctx = self.builder.build(ordered, pad_blocks=block_bucket, row_order=row_order,
+                                 pad_mixed=(D, P, T, D + P))
+        ctx.max_ctx_len = block_bucket * self.cache.page_size
+        ctx.max_q_len = max(1, T - D)
+        return self.model.forward(ctx, self.cache.views())[:ctx.n_wanted]
 
     def _run_repeated_shape(self, ordered: List[StepEntry], row_order=None) -> Optional[torch.Tensor]:
         """Steps with prompt portions: the second time the same shape comes (the same token
@@ -239,7 +320,7 @@ class ModelRunner:
         return logits[torch.tensor(rows, device=logits.device, dtype=torch.long)]
 
 
-def _capture(graph, fn):
+def _capture(graph, fn, pool=None):
     """Capture `fn` into `graph`.  Python's cyclic garbage collector must not run meanwhile:
     if it destroyed an older graph or freed device memory during the capture, the capture
     would be invalidated (and a graph destroyed from a destructor aborts the process), so
@@ -253,12 +334,34 @@ def _capture(graph, fn):
         clear()
     was_enabled = gc.isenabled()
     gc.disable()
+    # `torch.cuda.graph` would also give every cached block back to the driver first
+    # (`empty_cache`), after which the steps that follow pay for fresh allocations, by
+    # milliseconds and not the same every time: the capture is begun and ended by hand
+    global _capture_stream
+    if _capture_stream is None:
+        _capture_stream = torch.cuda.Stream()
+    _capture_stream.wait_stream(torch.cuda.current_stream())
     try:
-        with torch.cuda.graph(graph):
-            return fn()
+        with torch.cuda.stream(_capture_stream):
+            # one memory pool for all of a runner's graphs: a later capture finds the blocks of
+            # an earlier one's dead intermediates instead of asking the driver for new ones
+            # (outputs that a graph object still holds are live and are not handed out again)
+            if pool is not None:
+                graph.capture_begin(pool=pool)
+            else:
+                graph.capture_begin()
+            try:
+                out = fn()
+            finally:
+                graph.capture_end()
+        torch.cuda.current_stream().wait_stream(_capture_stream)
+        return out
     finally:
         if was_enabled:
             gc.enable()
+
+
+_capture_stream = None
 
 
 class _DecodeGraph:
@@ -304,10 +407,11 @@ class _DecodeGraph:
             graph = torch.cuda.CUDAGraph()
             self.capturing = True
             try:
-                self.logits = _capture(graph, lambda: model.forward(ctx, views))
+                self.logits = _capture(graph, lambda: model.forward(ctx, views), self.runner.graph_pool())
             finally:
                 self.capturing = False
             self.graph = graph
+            self.runner.captures += 1
             self.kernels_per_replay = model.ops.launches - launches
         else:
             ctx = self._build(entries)
@@ -316,6 +420,59 @@ class _DecodeGraph:
         self.graph.replay()
         model.ops.launches += self.kernels_per_replay
         return self.logits
+
+
+class _MixedGraph:
+    """A captured launch sequence for steps of any mixture padded to (D single-token requests,
+    P prompt portions, T tokens, block tables `block_bucket` wide): `BatchBuilder.build` with
+    `pad_mixed`.  Its index arrays live at fixed addresses; a step refills them and replays.
+    Launch sizes that depend on a portion's length or a context's are taken from the padded
+    sizes, so that they cover every later replay."""
+
+    def __init__(self, runner: ModelRunner, key):
+        self.runner = weakref.proxy(runner)     # no cycle: graphs die with their runner
+        self.D, self.P, self.T, self.block_bucket = key
+        R, W = self.D + self.P, self.D + self.P
+        n_groups = len(runner.cache.groups)
+        words = 4 * self.T + 8 * R + W + 64 + n_groups * (self.T + R * self.block_bucket + 8)
+        self.host = torch.empty(words, dtype=torch.int32, pin_memory=True)
+        self.dev = torch.empty(words, dtype=torch.int32, device=runner.device)
+        self.graph = None
+        self.logits = None
+        self.broken = False
+        self.capturing = False
+        self.kernels_per_replay = 0
+
+    def _build(self, entries, row_order=None) -> StepContext:
+        runner = self.runner
+        ctx = runner.builder.build(entries, pad_blocks=self.block_bucket,
+                                   buffers=(self.host, self.dev), row_order=row_order,
+                                   pad_mixed=(self.D, self.P, self.T, self.D + self.P))
+        ctx.max_ctx_len = self.block_bucket * runner.cache.page_size
+        ctx.max_q_len = max(1, self.T - self.D)
+        return ctx
+
+    def run(self, entries, row_order=None) -> torch.Tensor:
+        model, views = self.runner.model, self.runner.cache.views()
+        if self.graph is None:
+            # no warm-up run: a step of these padded sizes has already run once, kernel by
+            # kernel (`_padded_eagerly`), so the matrix library has met the shapes
+            ctx = self._build(entries, row_order)
+            launches = model.ops.launches
+            graph = torch.cuda.CUDAGraph()
+            self.capturing = True
+            try:
+                self.logits = _capture(graph, lambda: model.forward(ctx, views), self.runner.graph_pool())
+            finally:
+                self.capturing = False
+            self.graph = graph
+            self.runner.captures += 1
+            self.kernels_per_replay = model.ops.launches - launches
+        else:
+            ctx = self._build(entries, row_order)
+        self.graph.replay()
+        model.ops.launches += self.kernels_per_replay
+        return self.logits[:ctx.n_wanted]
 
 
 class _ShapeGraph:
@@ -351,10 +508,12 @@ class _ShapeGraph:
             self.capturing = True
             try:
                 self.logits = _capture(
-                    graph, lambda: runner.model.forward(ctx, runner.cache.views()))
+                    graph, lambda: runner.model.forward(ctx, runner.cache.views()),
+                    runner.graph_pool())
             finally:
                 self.capturing = False
             self.graph = graph
+            runner.captures += 1
             self.kernels_per_replay = runner.model.ops.launches - launches
         self.graph.replay()
         runner.model.ops.launches += self.kernels_per_replay

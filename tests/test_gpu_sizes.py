@@ -375,7 +375,8 @@ def test_preemption_lookahead_and_portion_graphs_in_bfloat16(tmp_path_factory):
     ahead = gen.complete_batch(prompts, roomy, arrival_steps=[0, 0, 1, 2, 4])
     assert ahead == plain_run
     runner = gen._runner
-    assert runner.graph_steps > 0 and len(runner._shape_graphs) > 0 and runner.capture_failures == 0
+    assert runner.graph_steps > 0 and runner.capture_failures == 0
+    assert len(runner._shape_graphs) + len(runner._mixed_graphs) > 0      # prompt portions replayed too
     squeezed = gen.complete_batch(prompts, tight, arrival_steps=[0, 0, 1, 2, 4])
     assert gen.last_result.stats.preemptions > 0
     assert all(len(o) == 40 for o in squeezed)
