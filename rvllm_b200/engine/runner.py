@@ -151,7 +151,7 @@ class ModelRunner:
         the requests are: in live traffic exact shapes hardly ever come twice, and a step of
         a small model launched kernel by kernel waits for the host (about 1.8 ms for some 140
         launches).  Returns None when this step has to go another way."""
-        if self.max_mixed_graphs <= 0:
+        if self.max_mixed_graphs < 0:             # off; 0: the padded layout without captures
             return None
         n_decode = 0
         while n_decode < len(ordered) and len(ordered[n_decode].tokens) == 1:

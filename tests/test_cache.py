@@ -148,3 +148,56 @@ def test_random_orders_keep_every_page_accounted_for(seed):
         m.free(rid)
     assert all(g.pool.in_use == 0 for g in m.groups) and m.slots.in_use == 0
     assert m.groups[0].pool.total_allocs > m.groups[0].pool.num_pages      # reuse happened
+
+
+def test_padded_mixture_layout():
+    """`BatchBuilder.build(pad_mixed=(D, P, T, W))`: the real single-token requests come first
+    among D, the real portions first among P, the last (empty) portion owns the filling tokens
+    and has no context, nothing that is padding writes a cache slot, and the wanted rows come
+    first among W."""
+    import numpy as np
+    import torch
+
+    from rvllm_b200.cache import CacheManager
+    from rvllm_b200.engine import BatchBuilder, StepEntry
+    from rvllm_b200.parts.base import PagedNeed, StateNeed
+    cache = CacheManager([PagedNeed(2, 16, None), StateNeed((2, 8))], [None, None], 8, 64, 8,
+                         dtype=torch.float32, device="cpu", allocate=False)
+    builder = BatchBuilder(cache, None, "cpu", pinned=False)
+    for rid, done in (("a", 20), ("b", 7), ("c", 0), ("d", 30)):
+        cache.add(rid)
+        cache.reserve(rid, done)
+        cache.advance(rid, done)
+    entries = [StepEntry("a", [11], (0,)), StepEntry("b", [12], (0,)),
+               StepEntry("c", list(range(100, 119)), ()), StepEntry("d", list(range(200, 205)), (4,))]
+    for e in entries:
+        cache.reserve(e.req, cache.requests[e.req].computed + len(e.tokens))
+    ctx = builder.build(entries, pad_blocks=16, pad_mixed=(4, 4, 64, 8))
+    assert (ctx.n_reqs, ctx.n_tokens, ctx.n_decode, ctx.n_wanted) == (8, 64, 4, 3)
+    q_start = ctx.q_start.numpy()
+    assert q_start.tolist() == [0, 1, 2, 3, 4, 23, 28, 28, 64]
+    assert ctx.ctx_lens.numpy().tolist() == [21, 8, 0, 0, 19, 35, 0, 0]
+    assert ctx.start_pos.numpy().tolist() == [20, 7, 0, 0, 0, 30, 0, 0]
+    slots = ctx.state_slot.numpy()
+    assert (slots[[2, 3, 6, 7]] == -1).all() and (slots[[0, 1, 4, 5]] >= 0).all()
+    tok = ctx.token_ids.numpy()
+    assert tok[:4].tolist() == [11, 12, 0, 0] and tok[4:23].tolist() == list(range(100, 119))
+    assert tok[23:28].tolist() == list(range(200, 205)) and (tok[28:] == 0).all()
+    assert ctx.positions.numpy()[23:28].tolist() == [30, 31, 32, 33, 34]
+    treq = ctx.token_req.numpy()
+    assert treq[:4].tolist() == [0, 1, 2, 3] and (treq[4:23] == 4).all() and (treq[28:] == 7).all()
+    assert ctx.logit_rows.numpy().tolist() == [0, 1, 27, 0, 0, 0, 0, 0]
+    g = ctx.groups[0]
+    sm = g.slot_mapping.numpy()
+    assert (sm[2:4] == -1).all() and (sm[28:] == -1).all() and (sm[:2] >= 0).all() and (sm[4:28] >= 0).all()
+    table = g.block_table.numpy()
+    assert table.shape == (8, 16) and (table[[2, 3, 6, 7]] == -1).all()
+    assert (table[5, :5] >= 0).all() and (table[5, 5:] == -1).all()
+    # sizes that do not fit are refused
+    import pytest
+    with pytest.raises(ValueError):
+        builder.build(entries, pad_mixed=(1, 4, 64, 8))
+    with pytest.raises(ValueError):
+        builder.build(entries, pad_mixed=(4, 2, 64, 8))        # no empty portion for the filling
+    with pytest.raises(ValueError):
+        builder.build(entries, pad_mixed=(4, 4, 64, 2))

@@ -188,6 +188,79 @@ def test_repeated_portion_shapes_are_replayed(folders, plains, dtype):
     compare(got, plains["B"], reqs, dtype)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_padded_mixtures_are_replayed(folders, plains, name, dtype):
+    """Steps of decoded tokens beside prompt portions of ever different lengths, with only the
+    last row of a portion wanted (as the scheduler asks): they are padded to sizes that come
+    again, run kernel by kernel the first time and replayed from then on.  The logits are the
+    plain implementation's, and bit for bit the same whether a step was replayed or not."""
+    from rvllm_b200.engine import StepEntry
+    model, cfg = engine(folders, name, dtype)
+    rng = random.Random(21)
+    page = 8 if name == "A" else 16
+    lengths = {"p%d" % i: n for i, n in enumerate((150, 131, 170, 97))}
+    reqs = {rid: [rng.randrange(cfg.vocab_size) for _ in range(n + 14)] for rid, n in lengths.items()}
+
+    def schedule():
+        """Four requests; prompts fed in portions of changing size while the earlier requests
+        decode beside them."""
+        steps, done = [], {rid: 0 for rid in reqs}
+        live, order = [], list(reqs)
+        sizes = [33, 20, 41, 17, 29, 38, 23, 36, 19, 31, 27, 35, 22, 40, 18, 30]
+        k = 0
+        while order or live:
+            if order and (not live or len(steps) % 3 == 0):
+                live.append(order.pop(0))
+            entries = []
+            for rid in list(live):
+                left = lengths[rid] - done[rid]
+                if left > 0:                                   # a prompt portion
+                    n = min(left, sizes[k % len(sizes)]); k += 1
+                    entries.append((rid, reqs[rid][done[rid]:done[rid] + n], (n - 1,)))
+                    done[rid] += n
+                elif done[rid] < len(reqs[rid]):               # a decoded token
+                    entries.append((rid, reqs[rid][done[rid]:done[rid] + 1], (0,)))
+                    done[rid] += 1
+                if done[rid] == len(reqs[rid]):
+                    live.remove(rid)
+            steps.append(entries)
+        return steps
+
+    def run(max_graphs):
+        pages = sum(-(-len(v) // page) for v in reqs.values()) + 4
+        runner = runner_for(model, page, pages, graphs=True)
+        runner.max_mixed_graphs = max_graphs
+        got, pos = {}, {rid: 0 for rid in reqs}
+        for entries in schedule():
+            for rid, _, _ in entries:
+                if not runner.cache.has(rid):
+                    runner.add_request(rid)
+            logits = runner.step([StepEntry(*e) for e in entries]).to("cpu", torch.float32)
+            for row, (rid, toks, want) in zip(logits, entries):
+                got[(rid, pos[rid] + want[0])] = row.clone()
+                pos[rid] += len(toks)
+        for rid in reqs:
+            runner.end_request(rid)
+        model.ops.check_status()
+        return runner, got
+
+    replayed, got = run(64)
+    assert len(replayed._mixed_graphs) > 0 and replayed.graph_steps > 10 and replayed.capture_failures == 0
+    eager, same = run(0)                            # the padded layout, never captured
+    assert len(eager._mixed_graphs) == 0
+    assert got.keys() == same.keys()
+    for key in got:
+        assert torch.equal(got[key], same[key]), key
+    plain = plains[name]
+    for rid, ids in reqs.items():
+        ref = plain.logits(ids)
+        scale = float(ref.abs().max())
+        for (r, p), row in got.items():
+            if r == rid:
+                assert float((row - ref[p]).abs().max()) / scale <= BOUND[dtype], (rid, p)
+
+
 def test_scratch_outgrown_after_a_capture(folders, plains):
     """A captured decode step names the split-KV scratch by address.  When a later step
     needs a larger scratch, the old one must stay valid for the older graph: replay it
