@@ -39,7 +39,7 @@ class ModelRunner:
         self._seen_shapes = set()
         self.max_shape_graphs = 16
         self._mixed_graphs: Dict[tuple, "_MixedGraph"] = {}
-        self.max_mixed_graphs = int(os.environ.get("RVLLM_MIXED_GRAPHS", "24"))
+        self.max_mixed_graphs = int(os.environ.get("RVLLM_MIXED_GRAPHS", "32"))
         self.steps = 0
         self.graph_steps = 0
         self.captures = 0                # launch sequences captured so far
@@ -178,12 +178,20 @@ class ModelRunner:
                 if len(self._seen_shapes) > 4096:
                     self._seen_shapes.clear()
                 self._seen_shapes.add(seen)
-            if first_time or len(self._mixed_graphs) >= self.max_mixed_graphs:
+            if first_time or self.max_mixed_graphs == 0:
                 return self._padded_eagerly(ordered, row_order, key)
+            if len(self._mixed_graphs) >= self.max_mixed_graphs:
+                # room for the sizes that come now: the launch sequence not replayed for the
+                # longest time goes (nothing of it may still be running when its memory does)
+                oldest = min(self._mixed_graphs, key=lambda k: self._mixed_graphs[k].last_used)
+                torch.cuda.synchronize()
+                del self._mixed_graphs[oldest]
+                self._seen_shapes.discard(("mixed",) + oldest)
             g = _MixedGraph(self, key)
             self._mixed_graphs[key] = g
         if g.broken:
             return self._padded_eagerly(ordered, row_order, key)
+        g.last_used = self.steps
         try:
             logits = g.run(ordered, row_order)
         except RuntimeError as e:
@@ -432,6 +440,7 @@ class _MixedGraph:
     def __init__(self, runner: ModelRunner, key):
         self.runner = weakref.proxy(runner)     # no cycle: graphs die with their runner
         self.D, self.P, self.T, self.block_bucket = key
+        self.last_used = 0
         R, W = self.D + self.P, self.D + self.P
         n_groups = len(runner.cache.groups)
         words = 4 * self.T + 8 * R + W + 64 + n_groups * (self.T + R * self.block_bucket + 8)

@@ -247,6 +247,9 @@ def test_padded_mixtures_are_replayed(folders, plains, name, dtype):
 
     replayed, got = run(64)
     assert len(replayed._mixed_graphs) > 0 and replayed.graph_steps > 10 and replayed.capture_failures == 0
+    few, again = run(2)                             # room for two: the oldest goes, others come
+    assert len(few._mixed_graphs) <= 2 and few.captures > 2 and few.capture_failures == 0
+    assert all(torch.equal(got[key], again[key]) for key in got)
     eager, same = run(0)                            # the padded layout, never captured
     assert len(eager._mixed_graphs) == 0
     assert got.keys() == same.keys()
