@@ -40,6 +40,7 @@ class ModelRunner:
         self.max_shape_graphs = 16
         self._mixed_graphs: Dict[tuple, "_MixedGraph"] = {}
         self.max_mixed_graphs = int(os.environ.get("RVLLM_MIXED_GRAPHS", "32"))
+        self.mixed_graph_idle_steps = 1024
         self.steps = 0
         self.graph_steps = 0
         self.captures = 0                # launch sequences captured so far
@@ -181,9 +182,13 @@ class ModelRunner:
             if first_time or self.max_mixed_graphs == 0:
                 return self._padded_eagerly(ordered, row_order, key)
             if len(self._mixed_graphs) >= self.max_mixed_graphs:
-                # room for the sizes that come now: the launch sequence not replayed for the
-                # longest time goes (nothing of it may still be running when its memory does)
+                # room for the sizes that come now, if a launch sequence has not been replayed
+                # for a long time (capturing costs several steps' time: sizes that take turns
+                # must not push one another out); nothing of it may still be running when its
+                # memory goes
                 oldest = min(self._mixed_graphs, key=lambda k: self._mixed_graphs[k].last_used)
+                if self.steps - self._mixed_graphs[oldest].last_used < self.mixed_graph_idle_steps:
+                    return self._padded_eagerly(ordered, row_order, key)
                 torch.cuda.synchronize()
                 del self._mixed_graphs[oldest]
                 self._seen_shapes.discard(("mixed",) + oldest)

@@ -227,10 +227,11 @@ def test_padded_mixtures_are_replayed(folders, plains, name, dtype):
             steps.append(entries)
         return steps
 
-    def run(max_graphs):
+    def run(max_graphs, idle_steps=1024):
         pages = sum(-(-len(v) // page) for v in reqs.values()) + 4
         runner = runner_for(model, page, pages, graphs=True)
         runner.max_mixed_graphs = max_graphs
+        runner.mixed_graph_idle_steps = idle_steps
         got, pos = {}, {rid: 0 for rid in reqs}
         for entries in schedule():
             for rid, _, _ in entries:
@@ -247,7 +248,7 @@ def test_padded_mixtures_are_replayed(folders, plains, name, dtype):
 
     replayed, got = run(64)
     assert len(replayed._mixed_graphs) > 0 and replayed.graph_steps > 10 and replayed.capture_failures == 0
-    few, again = run(2)                             # room for two: the oldest goes, others come
+    few, again = run(2, idle_steps=0)               # room for two: the oldest goes, others come
     assert len(few._mixed_graphs) <= 2 and few.captures > 2 and few.capture_failures == 0
     assert all(torch.equal(got[key], again[key]) for key in got)
     eager, same = run(0)                            # the padded layout, never captured
