@@ -146,7 +146,7 @@ class ModelRunner:
     def _run_padded_mixture(self, ordered: List[StepEntry], row_order=None) -> Optional[torch.Tensor]:
         """Steps with prompt portions, padded to sizes that come again: D single-token
         requests (a power of two), P prompt portions (a power of two, one more than there
-        are), T tokens in all (a multiple of 64, of 128 above 512, of 256 above 2,048) and a
+        are), T tokens in all (a multiple of 64, of 128 above 1,024, of 256 above 4,096) and a
         block-table width as in single-token steps.  The second step that pads to the same
         sizes is captured, and every later one replayed, whatever the portions' lengths and
         the requests are: in live traffic exact shapes hardly ever come twice, and a step of
@@ -161,7 +161,7 @@ class ModelRunner:
         D = 0 if n_decode == 0 else 1 << (n_decode - 1).bit_length()
         P = 1 << n_prefill.bit_length()                  # a power of two above n_prefill
         tokens = D + sum(len(e.tokens) for e in ordered[n_decode:])
-        gran = 64 if tokens <= 512 else (128 if tokens <= 2048 else 256)
+        gran = 64 if tokens <= 1024 else (128 if tokens <= 4096 else 256)
         T = -(-tokens // gran) * gran
         W = D + P
         if sum(len(e.want) for e in ordered) > W:
