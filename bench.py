@@ -591,7 +591,7 @@ def run_kernels(args):
 
 
 def run_workload(name, verbose=False):
-    """One scheduler workload through `Engine.step`, after an untimed run of the same
+    """One scheduler workload through `Engine.step`, after two untimed runs of the same
     requests (the reference's bench discards a warm-up run too, src/bin/bench.rs:215-232;
     prompts are seeded uniform random ids like its own, src/bin/bench.rs:93-109; random
     weights never produce a meaningful stop token, so none is set and every request
