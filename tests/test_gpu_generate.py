@@ -67,6 +67,33 @@ def test_generator_keeps_its_pool_between_calls(folders):
     assert gen._runner.cache.num_pages == 11
 
 
+def test_random_workloads_equal_plain(folders):
+    """Rounds of three to eight requests with random prompt lengths, arrival steps, portion
+    sizes, token budgets and pool sizes (some so small that sequences are preempted), all
+    through one generator, so that pools, captured single-token steps and captured padded
+    mixtures are used again from round to round: float32 greedy tokens equal the plain
+    implementation's every time."""
+    from rvllm_b200 import GenerateOptions, Generator
+    plain = PlainModel(folders["B"])
+    gen = Generator.load(folders["B"], dtype="float32")
+    rng = random.Random(7)
+    preempted = replayed = 0
+    for _ in range(8):
+        n = rng.randrange(3, 9)
+        prompts = [[rng.randrange(900) for _ in range(rng.randrange(3, 140))] for _ in range(n)]
+        arrivals = sorted(rng.randrange(0, 12) for _ in range(n))
+        opts = GenerateOptions(max_tokens=rng.randrange(4, 30), block_size=16, stop_tokens=[],
+                               prefill_chunk=rng.choice([None, 16, 37, 64]),
+                               max_batched_tokens=rng.choice([48, 96, 8192]),
+                               num_blocks=rng.choice([None, None, 14, 20]))
+        outs = gen.complete_batch(prompts, opts, arrival_steps=arrivals)
+        assert outs == [plain.greedy(p, opts.max_tokens) for p in prompts]
+        preempted += gen.last_result.stats.preemptions
+        replayed += len(gen._runner._mixed_graphs)
+        assert gen._runner.capture_failures == 0
+    assert preempted > 0 and replayed > 0
+
+
 def test_stop_token_ends_and_is_stripped(folders):
     from rvllm_b200 import GenerateOptions, Generator
     plain = PlainModel(folders["A"])
