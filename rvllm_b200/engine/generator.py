@@ -153,6 +153,8 @@ class Generator:
         slots = min(len(prompts), opts.max_running) if opts.max_running else len(prompts)
         runner = self._runner_for(bs, num_blocks, max(1, slots), exact=opts.num_blocks is not None)
         num_blocks = runner.cache.num_pages
+        for rid in list(runner.cache.requests):       # left behind by a call that raised
+            runner.end_request(rid)
         cfg = SchedulerConfig(block_size=bs, num_blocks=num_blocks,
                               max_running=opts.max_running or (1 << 30),
                               max_num_batched_tokens=opts.max_batched_tokens,
